@@ -13,6 +13,7 @@ from dataclasses import dataclass
 from pathlib import Path
 from typing import Any, Callable, Mapping
 
+from .bopilorn import BopilornConfig, bopilorn_model_spec
 from .qwen2 import Qwen2Config, qwen2_model_spec
 from .rozesun import RozesunConfig, rozesun_model_spec
 from .spec import ModelSpec
@@ -83,3 +84,4 @@ def load_config(model_dir: str | Path):
 register_architecture(Qwen2Config.architecture, Qwen2Config.from_dict, qwen2_model_spec)
 register_architecture(ZazasunConfig.architecture, ZazasunConfig.from_dict, zazasun_model_spec)
 register_architecture(RozesunConfig.architecture, RozesunConfig.from_dict, rozesun_model_spec)
+register_architecture(BopilornConfig.architecture, BopilornConfig.from_dict, bopilorn_model_spec)

@@ -15,7 +15,8 @@
 // every reduction has a fixed lane order, so a row's result depends only on its own request's
 // cache: not on how the prompt was cut into steps, nor on the other rows of the batch.
 // This is the attention of the 32-bit path and the fallback of the bfloat16 path.
-// Accepts any head_dim <= 256, any head counts, any page size.
+// Accepts any head_dim <= 256, any head counts, any page size.  Values may have another size than
+// keys (value_dim <= 256): the value pool and the output rows then have value_dim entries per head.
 #include "common.cuh"
 
 namespace mlr {
@@ -31,16 +32,16 @@ attention_generic_kernel(const T* q, const T* k_pool,
                          const int* __restrict__ tile_seg, const int* __restrict__ tile_row0,
                          const int* __restrict__ seg_q_start, const int* __restrict__ seg_q_len,
                          const int* __restrict__ seg_pos0, const int* __restrict__ block_table, const int* __restrict__ seg_slot,
-                         int table_width, int heads, int kv_heads, int head_dim, int page_size,
+                         int table_width, int heads, int kv_heads, int head_dim, int value_dim, int page_size,
                          int window, float scale) {
   pdl_trigger();
   pdl_wait();
   extern __shared__ float shared[];
-  const int D = head_dim;
+  const int D = head_dim, DV = value_dim;
   float* q_rows = shared;                                   // [16][D]
   float* k_tile = q_rows + ROWS_PER_TILE * D;               // [32][D+1]
-  float* v_tile = k_tile + KEYS_PER_TILE * (D + 1);         // [32][D]
-  float* p_tile = v_tile + KEYS_PER_TILE * D;               // [4 warps][4 rows][32]
+  float* v_tile = k_tile + KEYS_PER_TILE * (D + 1);         // [32][DV]
+  float* p_tile = v_tile + KEYS_PER_TILE * DV;              // [4 warps][4 rows][32]
 
   const int tile = blockIdx.x, head = blockIdx.y;
   const int kv_head = head / (heads / kv_heads);
@@ -71,17 +72,22 @@ attention_generic_kernel(const T* q, const T* k_pool,
     for (int idx = threadIdx.x; idx < KEYS_PER_TILE * D; idx += blockDim.x) {
       const int j = idx / D, d = idx - j * D;
       const int key = k0 + j;
-      float kv = 0.f, vv = 0.f;
+      float kv = 0.f;
       if (key <= last_pos) {
         const int page = table[key / page_size];
-        if (page >= 0) {
-          const size_t at = (((size_t)page * kv_heads + kv_head) * page_size + key % page_size) * D + d;
-          kv = to_float(k_pool[at]);
-          vv = to_float(v_pool[at]);
-        }
+        if (page >= 0) kv = to_float(k_pool[(((size_t)page * kv_heads + kv_head) * page_size + key % page_size) * D + d]);
       }
       k_tile[j * (D + 1) + d] = kv;
-      v_tile[j * D + d] = vv;
+    }
+    for (int idx = threadIdx.x; idx < KEYS_PER_TILE * DV; idx += blockDim.x) {
+      const int j = idx / DV, d = idx - j * DV;
+      const int key = k0 + j;
+      float vv = 0.f;
+      if (key <= last_pos) {
+        const int page = table[key / page_size];
+        if (page >= 0) vv = to_float(v_pool[(((size_t)page * kv_heads + kv_head) * page_size + key % page_size) * DV + d]);
+      }
+      v_tile[j * DV + d] = vv;
     }
     __syncthreads();
 
@@ -109,9 +115,9 @@ attention_generic_kernel(const T* q, const T* k_pool,
 #pragma unroll
       for (int c = 0; c < MAX_HEAD_DIM / 32; ++c) {
         const int d = lane + 32 * c;
-        if (d < D) {
+        if (d < DV) {
           float a = acc[i][c] * alpha;
-          for (int j = 0; j < KEYS_PER_TILE; ++j) a = fmaf(pw[j], v_tile[j * D + d], a);
+          for (int j = 0; j < KEYS_PER_TILE; ++j) a = fmaf(pw[j], v_tile[j * DV + d], a);
           acc[i][c] = a;
         }
       }
@@ -124,11 +130,11 @@ attention_generic_kernel(const T* q, const T* k_pool,
     const int r = warp * 4 + i;
     if (r >= rows) continue;
     const float inv = 1.f / l[i];
-    T* dst = out + ((size_t)(q_start + row0 + r) * heads + head) * D;
+    T* dst = out + ((size_t)(q_start + row0 + r) * heads + head) * DV;
 #pragma unroll
     for (int c = 0; c < MAX_HEAD_DIM / 32; ++c) {
       const int d = lane + 32 * c;
-      if (d < D) dst[d] = from_float<T>(acc[i][c] * inv);
+      if (d < DV) dst[d] = from_float<T>(acc[i][c] * inv);
     }
   }
 }
@@ -137,10 +143,10 @@ template <typename T>
 int attention_generic_launch(const void* q, const void* k_pool, const void* v_pool, void* out,
                              const int* tile_seg, const int* tile_row0, const int* seg_q_start,
                              const int* seg_q_len, const int* seg_pos0, const int* block_table, const int* seg_slot,
-                             int table_width, int tiles, int heads, int kv_heads, int head_dim,
+                             int table_width, int tiles, int heads, int kv_heads, int head_dim, int value_dim,
                              int page_size, int window, float scale, cudaStream_t stream) {
   const size_t shared = sizeof(float) * ((size_t)ROWS_PER_TILE * head_dim + (size_t)KEYS_PER_TILE * (head_dim + 1) +
-                                         (size_t)KEYS_PER_TILE * head_dim + 16 * KEYS_PER_TILE);
+                                         (size_t)KEYS_PER_TILE * value_dim + 16 * KEYS_PER_TILE);
   if (shared > 48 * 1024) {
     cudaError_t err = cudaFuncSetAttribute(attention_generic_kernel<T>,
                                            cudaFuncAttributeMaxDynamicSharedMemorySize, (int)shared);
@@ -149,7 +155,7 @@ int attention_generic_launch(const void* q, const void* k_pool, const void* v_po
   dim3 grid(tiles, heads);
   launch_kernel(attention_generic_kernel<T>, dim3(grid), dim3(128), shared, stream, 
       (const T*)q, (const T*)k_pool, (const T*)v_pool, (T*)out, tile_seg, tile_row0, seg_q_start,
-      seg_q_len, seg_pos0, block_table, seg_slot, table_width, heads, kv_heads, head_dim, page_size, window, scale);
+      seg_q_len, seg_pos0, block_table, seg_slot, table_width, heads, kv_heads, head_dim, value_dim, page_size, window, scale);
   return launch_status();
 }
 
@@ -159,27 +165,28 @@ using namespace mlr;
 
 MLR_DEFINE_PDL_SWITCH
 
-// q, out: [rows, heads, head_dim]; pools: [pages, kv_heads, page_size, head_dim].
+// q: [rows, heads, head_dim]; out: [rows, heads, value_dim]; pools: [pages, kv_heads, page_size, head_dim]
+// (keys) and [pages, kv_heads, page_size, value_dim] (values).
 // tile_seg/tile_row0: one entry per CTA tile of up to 16 rows of one segment.
 // window <= 0 means every earlier key is visible.
 MLR_EXPORT int mlr_attention_generic(const void* q, const void* k_pool, const void* v_pool, void* out,
                                      const int* tile_seg, const int* tile_row0, const int* seg_q_start,
                                      const int* seg_q_len, const int* seg_pos0, const int* block_table, const int* seg_slot,
-                                     int table_width, int tiles, int heads, int kv_heads, int head_dim,
+                                     int table_width, int tiles, int heads, int kv_heads, int head_dim, int value_dim,
                                      int page_size, int window, float scale, int dtype,
                                      cudaStream_t stream) {
   if (tiles == 0) return MLR_OK;
   if (tiles < 0 || heads <= 0 || kv_heads <= 0 || heads % kv_heads != 0 || head_dim <= 0 ||
-      page_size <= 0 || table_width <= 0)
+      value_dim <= 0 || page_size <= 0 || table_width <= 0)
     return MLR_BAD_SIZE;
-  if (head_dim > MAX_HEAD_DIM || heads > 65535) return MLR_TOO_LARGE;
+  if (head_dim > MAX_HEAD_DIM || value_dim > MAX_HEAD_DIM || heads > 65535) return MLR_TOO_LARGE;
   if (dtype == MLR_F32)
     return attention_generic_launch<float>(q, k_pool, v_pool, out, tile_seg, tile_row0, seg_q_start,
                                            seg_q_len, seg_pos0, block_table, seg_slot, table_width, tiles, heads,
-                                           kv_heads, head_dim, page_size, window, scale, stream);
+                                           kv_heads, head_dim, value_dim, page_size, window, scale, stream);
   if (dtype == MLR_BF16)
     return attention_generic_launch<bf16>(q, k_pool, v_pool, out, tile_seg, tile_row0, seg_q_start,
                                           seg_q_len, seg_pos0, block_table, seg_slot, table_width, tiles, heads,
-                                          kv_heads, head_dim, page_size, window, scale, stream);
+                                          kv_heads, head_dim, value_dim, page_size, window, scale, stream);
   return MLR_BAD_DTYPE;
 }

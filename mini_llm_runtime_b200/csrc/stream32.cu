@@ -1,7 +1,7 @@
 // Kernels of decoders whose residual stream is 32-bit floats and whose sublayers are wrapped in
 // layer norms on both sides ("sandwich" arrangement).
 //
-// mlr_embedding_rows32     float32 rows table[ids] of a table in the compute dtype.
+// mlr_embedding_rows32     float32 rows table[ids] * scale of a table in the compute dtype.
 // mlr_layer_norm_step      one pass over each row of the stream x that does, in this order, whatever
 //                          its arguments ask for:
 //                            x += LN(delta; dw, db)      the sublayer output that was still to be added,
@@ -20,7 +20,7 @@ namespace mlr {
 template <typename T>
 __global__ void __launch_bounds__(256)
 embedding_rows32_kernel(const int* __restrict__ ids, const T* __restrict__ table, float* __restrict__ out, int width,
-                        int vocab) {
+                        int vocab, float scale) {
   pdl_trigger();
   pdl_wait();
   const int row = blockIdx.x;
@@ -28,7 +28,7 @@ embedding_rows32_kernel(const int* __restrict__ ids, const T* __restrict__ table
   id = min(max(id, 0), vocab - 1);
   const T* src = table + (size_t)id * width;
   float* dst = out + (size_t)row * width;
-  for (int d = threadIdx.x; d < width; d += blockDim.x) dst[d] = to_float(src[d]);
+  for (int d = threadIdx.x; d < width; d += blockDim.x) dst[d] = to_float(src[d]) * scale;
 }
 
 // mean and 1/sqrt(var + eps) of `width` floats in shared memory; every thread gets both.
@@ -303,13 +303,13 @@ using namespace mlr;
 MLR_DEFINE_PDL_SWITCH
 
 MLR_EXPORT int mlr_embedding_rows32(const int* ids, const void* table, float* out, int rows, int width, int vocab,
-                                    int dtype, cudaStream_t stream) {
+                                    float scale, int dtype, cudaStream_t stream) {
   if (rows == 0) return MLR_OK;
   if (rows < 0 || width <= 0 || vocab <= 0) return MLR_BAD_SIZE;
   if (dtype == MLR_F32)
-    launch_kernel(embedding_rows32_kernel<float>, dim3(rows), dim3(256), 0, stream, ids, (const float*)table, out, width, vocab);
+    launch_kernel(embedding_rows32_kernel<float>, dim3(rows), dim3(256), 0, stream, ids, (const float*)table, out, width, vocab, scale);
   else if (dtype == MLR_BF16)
-    launch_kernel(embedding_rows32_kernel<bf16>, dim3(rows), dim3(256), 0, stream, ids, (const bf16*)table, out, width, vocab);
+    launch_kernel(embedding_rows32_kernel<bf16>, dim3(rows), dim3(256), 0, stream, ids, (const bf16*)table, out, width, vocab, scale);
   else
     return MLR_BAD_DTYPE;
   return launch_status();

@@ -48,6 +48,8 @@ LIBRARIES: dict[str, tuple[str, ...]] = {
     "stream32": (),
     "attention_latent": (),
     "attention_latent_mma": (),
+    "attention_rotated": (),
+    "routed_experts": (),
 }
 
 _loaded: dict[str, ctypes.CDLL] = {}

@@ -615,19 +615,23 @@ class CudaOps:
 
     def paged_attention(self, q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor,
                         batch: AttentionBatch, num_heads: int, num_kv_heads: int, head_dim: int,
-                        scale: float, window: int | None) -> torch.Tensor:
-        """Causal attention of every row of the step over its request's cached keys."""
+                        scale: float, window: int | None, value_dim: int | None = None) -> torch.Tensor:
+        """Causal attention of every row of the step over its request's cached keys.  ``value_dim``:
+        the size of a value head where it differs from a key head's (the result then has
+        ``num_heads * value_dim`` columns; only the generic kernel takes that)."""
         _need(q, "q", dims=2)
         _need(k_pool, "k_pool", q.dtype, 4)
         _need(v_pool, "v_pool", q.dtype, 4)
+        value_dim = head_dim if value_dim is None else int(value_dim)
         if q.shape[1] != num_heads * head_dim:
             raise KernelError(f"q rows have {q.shape[1]} entries, expected {num_heads * head_dim}")
-        if k_pool.shape[1] != num_kv_heads or k_pool.shape[3] != head_dim or k_pool.shape != v_pool.shape:
-            raise KernelError(f"page pools have shape {tuple(k_pool.shape)}, expected "
-                              f"[pages, {num_kv_heads}, page_size, {head_dim}]")
+        if (k_pool.shape[1] != num_kv_heads or k_pool.shape[3] != head_dim or k_pool.shape[:3] != v_pool.shape[:3]
+                or v_pool.shape[3] != value_dim):
+            raise KernelError(f"page pools have shapes {tuple(k_pool.shape)} and {tuple(v_pool.shape)}, expected "
+                              f"[pages, {num_kv_heads}, page_size, {head_dim}] and [.., {value_dim}]")
         if "tile_seg" not in batch.plan:
             raise KernelError("the batch carries no attention work lists (plan_attention)")
-        out = torch.empty_like(q)
+        out = torch.empty((q.shape[0], num_heads * value_dim), dtype=q.dtype, device=q.device)
         plan, counts = batch.plan, batch.counts
         generic_tiles = counts["tiles"]
         group = num_heads // num_kv_heads
@@ -635,7 +639,8 @@ class CudaOps:
         paged_by_tma = page_size >= 8 and page_size & (page_size - 1) == 0
         common = (_ptr(batch.seg_q_start), _ptr(batch.seg_q_len), _ptr(batch.seg_pos0), _ptr(batch.block_table),
                   _ptr(batch.seg_slot), batch.block_table.shape[1])
-        if (self.use_mma_attention and q.dtype == torch.bfloat16 and head_dim in (64, 128) and group <= 16
+        equal_sizes = value_dim == head_dim
+        if (self.use_mma_attention and equal_sizes and q.dtype == torch.bfloat16 and head_dim in (64, 128) and group <= 16
                 and batch.num_decode * num_kv_heads <= self.ATTENTION_COUNTERS):
             if batch.num_decode > 0:
                 self._decode_attention(q, k_pool, v_pool, out, batch, num_heads, num_kv_heads, head_dim, scale,
@@ -667,7 +672,7 @@ class CudaOps:
                     num_kv_heads, head_dim, page_size, int(window or 0), ctypes.c_float(scale), _stream()),
                     "prefill attention")
             return out
-        if (self.use_decode_kernel and batch.num_decode > 0
+        if (self.use_decode_kernel and batch.num_decode > 0 and equal_sizes
                 and q.dtype == torch.bfloat16 and head_dim in (64, 128) and group <= 8
                 and batch.num_decode * num_kv_heads <= self.ATTENTION_COUNTERS):
             self._decode_attention(q, k_pool, v_pool, out, batch, num_heads, num_kv_heads, head_dim, scale, window)
@@ -675,7 +680,7 @@ class CudaOps:
         if generic_tiles > 0:
             _check(build.load_library("attention_generic").mlr_attention_generic(
                 _ptr(q), _ptr(k_pool), _ptr(v_pool), _ptr(out), _ptr(plan["tile_seg"]), _ptr(plan["tile_row0"]),
-                *common, generic_tiles, num_heads, num_kv_heads, head_dim,
+                *common, generic_tiles, num_heads, num_kv_heads, head_dim, value_dim,
                 page_size, int(window or 0), ctypes.c_float(scale), _code(q.dtype), _stream()),
                 "paged_attention")
         return out
@@ -998,14 +1003,14 @@ class CudaOps:
         return out
 
     # ------------------------------------------------------------------ 32-bit stream with layer norms
-    def embedding_rows32(self, ids: torch.Tensor, table: torch.Tensor) -> torch.Tensor:
-        """float32 rows table[ids] of a table in the compute dtype."""
+    def embedding_rows32(self, ids: torch.Tensor, table: torch.Tensor, scale: float = 1.0) -> torch.Tensor:
+        """float32 rows table[ids] * scale of a table in the compute dtype."""
         _need(ids, "ids", torch.int32, 1)
         _need(table, "table", dims=2)
         out = torch.empty((ids.shape[0], table.shape[1]), dtype=torch.float32, device=table.device)
         _check(build.load_library("stream32").mlr_embedding_rows32(
-            _ptr(ids), _ptr(table), _ptr(out), ids.shape[0], table.shape[1], table.shape[0], _code(table.dtype),
-            _stream()), "embedding_rows32")
+            _ptr(ids), _ptr(table), _ptr(out), ids.shape[0], table.shape[1], table.shape[0], ctypes.c_float(scale),
+            _code(table.dtype), _stream()), "embedding_rows32")
         return out
 
     def layer_norm_step(self, x: torch.Tensor, eps: float, *, delta: torch.Tensor | None = None, delta_norm=None,
@@ -1240,6 +1245,121 @@ class CudaOps:
         return cache[(rank, rot)]
 
     # ------------------------------------------------------------------ sampling
+    # ------------------------------------------------------------------ attention with normalised, turned values
+    def rotated_prepare(self, qkv: torch.Tensor, positions: torch.Tensor, q_weight: torch.Tensor | None,
+                        k_weight: torch.Tensor | None, eps: float, key_freq: torch.Tensor, magnitude: float,
+                        value_freq: torch.Tensor | None, interleaved: bool, normalise_values: bool,
+                        slots: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, heads: int, kv_heads: int,
+                        dim: int, vdim: int, write_kv: bool = True) -> torch.Tensor:
+        """From float32 rows [q | k | v]: q and k RMS-normalised over their whole projections (weights
+        ``q_weight`` / ``k_weight``, None: not normalised) and turned over their first 2 * len(key_freq)
+        entries per head (sine and cosine times ``magnitude``); every value head brought to unit root
+        mean square (``normalise_values``) and turned over all its entries by ``value_freq`` (None: not
+        turned); keys and values stored at ``slots``.  Returns q [rows, heads * dim] in the pools'
+        dtype."""
+        _need(qkv, "qkv", torch.float32, 2)
+        _need(positions, "positions", torch.int32, 1)
+        _need(key_freq, "key_freq", torch.float32, 1)
+        _need(slots, "slots", torch.int64, 1)
+        _need(k_pool, "k_pool", dims=4)
+        _need(v_pool, "v_pool", k_pool.dtype, 4)
+        rows = qkv.shape[0]
+        if qkv.shape[1] != (heads + kv_heads) * dim + kv_heads * vdim:
+            raise KernelError("qkv width does not match the head counts and sizes")
+        for name, weight, size in (("q_weight", q_weight, heads * dim), ("k_weight", k_weight, kv_heads * dim)):
+            if weight is not None:
+                _need(weight, name, torch.float32, 1)
+                if weight.shape[0] != size:
+                    raise KernelError(f"{name} holds {weight.shape[0]} entries, the projection has {size}")
+        if value_freq is not None:
+            _need(value_freq, "value_freq", torch.float32, 1)
+            if value_freq.shape[0] * 2 != vdim:
+                raise KernelError("value_freq needs one frequency per pair of value entries")
+        rot = 2 * key_freq.shape[0]
+        if rot > dim or positions.shape[0] != rows or slots.shape[0] != rows:
+            raise KernelError("at most dim turned entries; one position and one slot per row")
+        if (k_pool.shape[1] != kv_heads or k_pool.shape[3] != dim or v_pool.shape[:3] != k_pool.shape[:3]
+                or v_pool.shape[3] != vdim):
+            raise KernelError("page pools do not match the head sizes")
+        q = torch.empty((rows, heads * dim), dtype=k_pool.dtype, device=qkv.device)
+        _check(build.load_library("attention_rotated").mlr_rotated_prepare(
+            _ptr(qkv), _ptr(positions), _ptr(q_weight), _ptr(k_weight), _ptr(key_freq), _ptr(value_freq), _ptr(slots),
+            _ptr(q), _ptr(k_pool), _ptr(v_pool), rows, heads, kv_heads, dim, vdim, rot, int(bool(interleaved)),
+            int(bool(normalise_values)), ctypes.c_float(eps), ctypes.c_float(magnitude), k_pool.shape[2],
+            int(bool(write_kv)), _code(k_pool.dtype), _stream()), "rotated_prepare")
+        return q
+
+    def turn_heads(self, x: torch.Tensor, positions: torch.Tensor, freq: torch.Tensor, heads: int, dim: int,
+                   interleaved: bool, sign: float = 1.0) -> torch.Tensor:
+        """x [rows, heads * dim]: the first 2 * len(freq) entries of every head turned in place by
+        sign * position * freq[i]."""
+        _need(x, "x", dims=2)
+        _need(positions, "positions", torch.int32, 1)
+        _need(freq, "freq", torch.float32, 1)
+        if x.shape[1] != heads * dim or positions.shape[0] != x.shape[0] or 2 * freq.shape[0] > dim:
+            raise KernelError("turn_heads: rows of heads * dim entries, one position per row, at most dim turned entries")
+        _check(build.load_library("attention_rotated").mlr_turn_heads(
+            _ptr(x), _ptr(positions), _ptr(freq), x.shape[0], heads, dim, 2 * freq.shape[0], int(bool(interleaved)),
+            ctypes.c_float(sign), _code(x.dtype), _stream()), "turn_heads")
+        return x
+
+    # ------------------------------------------------------------------ routed experts
+    def route_experts(self, x: torch.Tensor, router: torch.Tensor, correction: torch.Tensor | None, top: int,
+                      groups: int = 1, keep: int = 1, scoring: str = "softmax",
+                      renormalise: bool = False) -> tuple[torch.Tensor, torch.Tensor]:
+        """Router of a mixture of experts, in float32: scores = softmax (or sigmoid) of router x; the ``top``
+        largest of scores + correction among the experts of the ``keep`` best of ``groups`` groups are
+        chosen (int32 [rows, top]); their weights are their scores (float32 [rows, top]), divided by
+        their sum with ``renormalise``."""
+        _need(x, "x", dims=2)
+        _need(router, "router", torch.float32, 2)
+        experts = router.shape[0]
+        if router.shape[1] != x.shape[1]:
+            raise KernelError("the router needs one column per input column")
+        if correction is not None:
+            _need(correction, "correction", torch.float32, 1)
+            if correction.shape[0] != experts:
+                raise KernelError("one correction per expert")
+        if scoring not in ("softmax", "sigmoid"):
+            raise KernelError(f"unknown router scoring {scoring!r}")
+        chosen = torch.empty((x.shape[0], top), dtype=torch.int32, device=x.device)
+        weights = torch.empty((x.shape[0], top), dtype=torch.float32, device=x.device)
+        _check(build.load_library("routed_experts").mlr_route_experts(
+            _ptr(x), _ptr(router), _ptr(correction), _ptr(chosen), _ptr(weights), x.shape[0], x.shape[1], experts,
+            int(top), int(groups), int(keep), int(scoring == "sigmoid"), int(bool(renormalise)), _code(x.dtype),
+            _stream()), "route_experts")
+        return chosen, weights
+
+    def routed_experts(self, x: torch.Tensor, chosen: torch.Tensor, weights: torch.Tensor, gate_up: torch.Tensor,
+                       down: torch.Tensor, block: int, activation: str = "silu") -> torch.Tensor:
+        """sum_t weights[r, t] * down_e(act(gate_e x_r) * up_e x_r), e = chosen[r, t], as float32 [rows, N].
+        ``gate_up`` [experts, 2 * inner, K] holds blocks of ``block`` gate rows followed by the up rows
+        of the same outputs, ``down`` [experts, N, inner]."""
+        _need(x, "x", dims=2)
+        _need(chosen, "chosen", torch.int32, 2)
+        _need(weights, "weights", torch.float32, 2)
+        _need(gate_up, "gate_up", x.dtype, 3)
+        _need(down, "down", x.dtype, 3)
+        rows, K = x.shape
+        experts, inner, top = gate_up.shape[0], gate_up.shape[1] // 2, chosen.shape[1]
+        N = down.shape[1]
+        if (gate_up.shape[2] != K or down.shape[0] != experts or down.shape[2] != inner or gate_up.shape[1] % 2
+                or chosen.shape != (rows, top) or weights.shape != (rows, top) or block <= 0 or inner % block):
+            raise KernelError("routed_experts: shapes do not fit")
+        if activation not in ("silu", "gelu_tanh"):
+            raise KernelError(f"unknown gate activation {activation!r}")
+        act = 1 if activation == "gelu_tanh" else 0
+        out = torch.empty((rows, N), dtype=torch.float32, device=x.device)
+        if rows == 0:
+            return out
+        lib = build.load_library("routed_experts")
+        hidden = torch.empty((rows * top, inner), dtype=x.dtype, device=x.device)
+        _check(lib.mlr_expert_hidden(_ptr(x), _ptr(chosen), _ptr(gate_up), _ptr(hidden), rows, K, inner, top, int(block),
+                                     act, _code(x.dtype), _stream()), "expert_hidden")
+        _check(lib.mlr_expert_down(_ptr(hidden), _ptr(chosen), _ptr(weights), _ptr(down), _ptr(out), rows, N, inner,
+                                   top, _code(x.dtype), _stream()), "expert_down")
+        return out
+
     def sample(self, logits: torch.Tensor, temperatures: torch.Tensor, seeds: torch.Tensor,
                counters: torch.Tensor) -> torch.Tensor:
         """One token per row of float32 logits: argmax where temperature <= 0, else a draw from

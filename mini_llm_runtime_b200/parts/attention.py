@@ -13,6 +13,7 @@ from __future__ import annotations
 import torch
 
 from .. import ops
+from ..config.spec import PartSpec
 from ..ops import AttentionBatch
 from .base import KVCacheNeed, Mixer, TensorSpec, build_part, register_part
 
@@ -200,5 +201,113 @@ class DifferentialAttention(Mixer):
         return k.linear(mixed, self.w_o, out_dtype=torch.float32)
 
 
+class RotatedValueAttention(Mixer):
+    """Grouped-query softmax attention over all earlier keys, with norms on q, k and v and a rotation
+    of the values.
+
+    q = Wq x [heads * dim], k = Wk x [kv_heads * dim], v = Wv x [kv_heads * vdim], no biases (one
+    fused product).  With ``qk_norm="projection"`` q and k are RMS-normalised over the whole projection
+    (all heads at once) with one learned weight per entry (``q.norm``, ``k.norm``); ``"none"`` leaves
+    them.  Then the first ``rope_dims`` entries of every q and k head are turned by the position
+    (``rope_layout`` ``interleaved``: pairs (2i, 2i + 1), ``half``: (i, i + rope_dims/2); base
+    ``rope_base``; ``rope_scaling`` optional, see ``PairedRope``).  ``value_norm``: every value head is
+    divided by its root mean square over vdim (no weight).  ``value_rotation``: the value of position j
+    is turned by j over all vdim entries (same pair layout, base ``rope_base``, never scaled) before
+    it is cached, and each head's output at position i is turned back by -i, so that the output
+    depends on the distances i - j only.  score = (q . k) * ``scale``; query head h reads kv head
+    h // (heads / kv_heads); Wo on the concatenated heads.
+
+    32-bit: the norms, angles and rotations, scores and softmax; the projections leave 32-bit rows.
+    In bfloat16 the products' operands, q, and the cached keys and values are bfloat16."""
+
+    graph_safe = True
+    plan_key = "paged_attention"
+
+    def __init__(self, spec, compute_dtype):
+        super().__init__(spec, compute_dtype)
+        a = self.args
+        self.hidden_size = int(a["hidden_size"])
+        self.heads = int(a["heads"])
+        self.kv_heads = int(a.get("kv_heads", self.heads))
+        self.dim = int(a["dim"])
+        self.vdim = int(a.get("vdim", self.dim))
+        self.scale = float(a["scale"])
+        self.eps = float(a["eps"])
+        self.qk_norm = str(a.get("qk_norm", "projection"))
+        if self.qk_norm not in ("projection", "none"):
+            raise ValueError(f"unknown q/k norm {self.qk_norm!r}; known: projection, none")
+        self.value_norm = bool(a.get("value_norm", True))
+        self.value_rotation = bool(a.get("value_rotation", True))
+        if self.heads % self.kv_heads:
+            raise ValueError("heads must be divisible by kv_heads")
+        layout = str(a.get("rope_layout", "interleaved"))
+        rope_dims = int(a.get("rope_dims", self.dim))
+        if rope_dims % 2 or not 0 < rope_dims <= self.dim:
+            raise ValueError("the rotation covers an even number of entries, at most dim")
+        self.position = build_part("position", PartSpec("rope_pairs", {
+            "head_dim": rope_dims, "theta": float(a["rope_base"]), "layout": layout,
+            "scaling": dict(a.get("rope_scaling") or {})}), compute_dtype)
+        self.value_position = None
+        if self.value_rotation:
+            if self.vdim % 2:
+                raise ValueError("values are turned in pairs: vdim must be even")
+            self.value_position = build_part("position", PartSpec("rope_pairs", {
+                "head_dim": self.vdim, "theta": float(a["rope_base"]), "layout": layout}), compute_dtype)
+        self.w_qkv = self.w_o = self.q_norm = self.k_norm = None
+
+    def cache_need(self):
+        return KVCacheNeed(self.kv_heads, self.dim, None, value_dim=None if self.vdim == self.dim else self.vdim)
+
+    def tensors(self):
+        p, h = self.prefix, self.hidden_size
+        out = {p + "q": TensorSpec((self.heads * self.dim, h)), p + "k": TensorSpec((self.kv_heads * self.dim, h)),
+               p + "v": TensorSpec((self.kv_heads * self.vdim, h)), p + "o": TensorSpec((h, self.heads * self.vdim))}
+        if self.qk_norm == "projection":
+            out[p + "q.norm"] = TensorSpec((self.heads * self.dim,), init="norm")
+            out[p + "k.norm"] = TensorSpec((self.kv_heads * self.dim,), init="norm")
+        return out
+
+    def load(self, tensors, device):
+        p = self.prefix
+        self.w_qkv = self._to_compute(torch.cat([tensors[p + n] for n in "qkv"], dim=0), device)
+        self.w_o = self._to_compute(tensors[p + "o"], device)
+        if self.qk_norm == "projection":
+            self.q_norm = tensors[p + "q.norm"].to(device=device, dtype=torch.float32).contiguous()
+            self.k_norm = tensors[p + "k.norm"].to(device=device, dtype=torch.float32).contiguous()
+        self.position.load({}, device)
+        if self.value_position is not None:
+            self.value_position.load({}, device)
+
+    def step_plan(self, host):
+        return ops.current().plan_attention(host.lengths, host.position_start)
+
+    def _batch(self, ctx, view) -> AttentionBatch:
+        batch = view.shared.get("attention_batch")
+        if batch is None:
+            arrays, counts = ctx.plans.get(self.plan_key, ({}, {}))
+            batch = AttentionBatch(
+                seg_q_start=ctx.seg_q_start, seg_q_len=ctx.seg_q_len, seg_pos0=ctx.seg_pos0, seg_slot=ctx.seg_slot,
+                block_table=view.block_table, num_segments=ctx.num_segments, max_q_len=ctx.max_q_len,
+                max_kv_len=ctx.max_kv_len, plan=arrays, counts=counts)
+            view.shared["attention_batch"] = batch
+        return batch
+
+    def forward(self, x, ctx, view, writes_cache):
+        k = ops.current()
+        interleaved = self.position.interleaved
+        value_freq = None if self.value_position is None else self.value_position.rotary_frequencies()
+        qkv = k.linear(x, self.w_qkv, out_dtype=torch.float32)
+        q = k.rotated_prepare(qkv, ctx.positions, self.q_norm, self.k_norm, self.eps,
+                              self.position.rotary_frequencies(), self.position.magnitude, value_freq, interleaved,
+                              self.value_norm, view.slots, view.k_pool, view.v_pool, self.heads, self.kv_heads,
+                              self.dim, self.vdim, writes_cache)
+        mixed = k.paged_attention(q, view.k_pool, view.v_pool, self._batch(ctx, view), self.heads, self.kv_heads,
+                                  self.dim, self.scale, None, value_dim=self.vdim)
+        if value_freq is not None:
+            mixed = k.turn_heads(mixed, ctx.positions, value_freq, self.heads, self.vdim, interleaved, sign=-1.0)
+        return k.linear(mixed, self.w_o, out_dtype=torch.float32)
+
+
 register_part("mixer", "gqa_attention", GQAAttention)
 register_part("mixer", "differential_attention", DifferentialAttention)
+register_part("mixer", "rotated_value_attention", RotatedValueAttention)

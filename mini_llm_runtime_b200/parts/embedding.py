@@ -25,6 +25,10 @@ class TokenEmbedding(Embedding):
         # model whose residual stream is 32-bit), the table itself stays in the compute dtype
         self.tensor = self.args.get("tensor") or self.prefix + "weight"
         self.float_rows = str(self.args.get("rows", "")) == "float32"
+        # ``scale``: every row is multiplied by it (in 32-bit; only with 32-bit rows)
+        self.scale = float(self.args.get("scale", 1.0))
+        if self.scale != 1.0 and not self.float_rows:
+            raise ValueError("a scaled embedding hands out 32-bit rows (rows=\"float32\")")
         self.weight: torch.Tensor | None = None
 
     def tensors(self):
@@ -35,7 +39,7 @@ class TokenEmbedding(Embedding):
 
     def forward(self, token_ids, positions=None):
         if self.float_rows:
-            return ops.current().embedding_rows32(token_ids, self.weight)
+            return ops.current().embedding_rows32(token_ids, self.weight, self.scale)
         return ops.current().embedding(token_ids, self.weight)
 
 

@@ -76,7 +76,8 @@ class LayerNorm(Norm):
       if given), stream += offset (a vector, if given), then this norm of the new stream.
 
     The checkpoint names come from the spec: ``tensor`` (weight) and ``tensor`` + ".b" (bias), unless
-    ``bias_tensor`` names it."""
+    ``bias_tensor`` names it.  With ``bias=False`` the norm has a weight only: the checkpoint holds no
+    bias and the kernels get a vector of zeros (adding 0 changes no bit)."""
 
     graph_safe = True
 
@@ -85,17 +86,23 @@ class LayerNorm(Norm):
         self.size = int(self.args["size"])
         self.eps = float(self.args["eps"])
         self.tensor = self.args.get("tensor") or self.prefix + "weight"
+        self.has_bias = bool(self.args.get("bias", True))
         self.bias_tensor = self.args.get("bias_tensor") or self.tensor + ".b"
         self.weight: torch.Tensor | None = None
         self.bias: torch.Tensor | None = None
 
     def tensors(self):
-        return {self.tensor: TensorSpec((self.size,), init="norm"),
-                self.bias_tensor: TensorSpec((self.size,), init="bias")}
+        out = {self.tensor: TensorSpec((self.size,), init="norm")}
+        if self.has_bias:
+            out[self.bias_tensor] = TensorSpec((self.size,), init="bias")
+        return out
 
     def load(self, tensors, device):
         self.weight = tensors[self.tensor].to(device=device, dtype=torch.float32).contiguous()
-        self.bias = tensors[self.bias_tensor].to(device=device, dtype=torch.float32).contiguous()
+        if self.has_bias:
+            self.bias = tensors[self.bias_tensor].to(device=device, dtype=torch.float32).contiguous()
+        else:
+            self.bias = torch.zeros(self.size, dtype=torch.float32, device=device)
 
     @property
     def pair(self):

@@ -9,6 +9,8 @@ positions is kept, so ``max_position_embeddings`` only bounds lengths, as in the
 
 from __future__ import annotations
 
+import math
+
 import torch
 
 from .. import ops
@@ -49,18 +51,43 @@ class PairedRope(RotateHalfRope):
     """The same rotation for mixers that turn a vector of ``head_dim`` numbers themselves (their
     kernels take ``rotary_frequencies()`` and ``interleaved``): pair i is (i, i + head_dim/2), or, with
     ``layout="interleaved"``, (2i, 2i + 1); it turns by position * theta^(-2i/head_dim).  The frequencies
-    are evaluated in 64-bit and rounded once."""
+    are evaluated in 64-bit and rounded once.
+
+    ``scaling`` = {factor, original, fast, slow} stretches the long wavelengths for contexts beyond the
+    ``original`` one: with pair(t) = head_dim * ln(original / (2 pi t)) / (2 ln theta) the index of the
+    pair that makes t turns over the original context, low = max(floor(pair(fast)), 0), high =
+    min(ceil(pair(slow)), head_dim - 1) and ramp_i = clamp((i - low) / max(high - low, 0.001), 0, 1), pair
+    i gets f_i / factor * ramp_i + f_i * (1 - ramp_i); ``magnitude`` = 0.1 ln(factor) + 1 multiplies
+    sine and cosine (1 without scaling)."""
 
     def __init__(self, spec, compute_dtype):
-        super().__init__(spec, compute_dtype)
-        layout = str(self.args.get("layout", "half"))
+        layout = str(spec.args.get("layout", "half"))
         if layout not in ("half", "interleaved"):
             raise ValueError(f"unknown pair layout {layout!r}; known: half, interleaved")
+        scaling = dict(spec.args.get("scaling") or {})
+        if scaling and any(name not in scaling for name in ("factor", "original", "fast", "slow")):
+            raise ValueError("a frequency scaling needs factor, original, fast and slow")
+        self.scaling = scaling
+        self.magnitude = 0.1 * math.log(float(scaling["factor"])) + 1.0 if scaling else 1.0
+        super().__init__(spec, compute_dtype)
         self.interleaved = layout == "interleaved"
 
     def _frequencies(self):
-        exponents = torch.arange(0, self.head_dim, 2, dtype=torch.float64) / self.head_dim
-        return (self.theta ** -exponents).to(torch.float32)
+        n = self.head_dim
+        exponents = torch.arange(0, n, 2, dtype=torch.float64) / n
+        plain = self.theta ** -exponents
+        if not self.scaling:
+            return plain.to(torch.float32)
+        factor, original = float(self.scaling["factor"]), float(self.scaling["original"])
+
+        def pair_of(turns: float) -> float:
+            return n * math.log(original / (2.0 * math.pi * turns)) / (2.0 * math.log(self.theta))
+
+        low = max(math.floor(pair_of(float(self.scaling["fast"]))), 0)
+        high = min(math.ceil(pair_of(float(self.scaling["slow"]))), n - 1)
+        index = torch.arange(n // 2, dtype=torch.float64)
+        ramp = ((index - low) / max(high - low, 0.001)).clamp(0.0, 1.0)
+        return (plain / factor * ramp + plain * (1.0 - ramp)).to(torch.float32)
 
     def rotate_and_store(self, qkv, ctx, view, num_heads, num_kv_heads, head_dim, write_kv):
         raise NotImplementedError("this encoding is applied by the mixer's own kernels")

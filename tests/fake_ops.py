@@ -148,10 +148,11 @@ class FakeOps:
                                write_kv)
         return self.paged_attention(q, k_pool, v_pool, batch, num_heads, num_kv_heads, head_dim, scale, window)
 
-    def paged_attention(self, q, k_pool, v_pool, batch, num_heads, num_kv_heads, head_dim, scale, window):
+    def paged_attention(self, q, k_pool, v_pool, batch, num_heads, num_kv_heads, head_dim, scale, window,
+                        value_dim=None):
         page_size = k_pool.shape[2]
         group = num_heads // num_kv_heads
-        out = torch.empty_like(q)
+        out = torch.empty((q.shape[0], num_heads * (value_dim or head_dim)), dtype=q.dtype)
         q3 = q.float().view(-1, num_heads, head_dim)
         for seg in range(batch.num_segments):
             start, length, pos0 = (int(batch.seg_q_start[seg]), int(batch.seg_q_len[seg]),
@@ -293,8 +294,8 @@ class FakeOps:
         return out
 
     # ---- 32-bit stream between layer norms, latent attention
-    def embedding_rows32(self, ids, table):
-        return table[ids.long()].float()
+    def embedding_rows32(self, ids, table, scale=1.0):
+        return table[ids.long()].float() * scale
 
     @staticmethod
     def _layer_norm(v, pair, eps):
@@ -387,4 +388,66 @@ class FakeOps:
                     scores = torch.cat([scores, sink[:, None]], dim=1)
                 weights = torch.softmax(scores, dim=-1)[:, :len(keys)]
                 out[start + r] = (weights @ rows[:, :rank]).reshape(-1)
+        return out
+
+    # ---- attention with normalised, turned values; routed experts
+    def rotated_prepare(self, qkv, positions, q_weight, k_weight, eps, key_freq, magnitude, value_freq, interleaved,
+                        normalise_values, slots, k_pool, v_pool, heads, kv_heads, dim, vdim, write_kv=True):
+        def normed(t, weight):
+            return t if weight is None else t * torch.rsqrt((t * t).mean(-1, keepdim=True) + eps) * weight
+
+        def turned(t, frequencies, factor):
+            full = self._turn(t, positions, frequencies, interleaved)
+            n = 2 * frequencies.shape[0]
+            if factor != 1.0:
+                full[..., :n] = full[..., :n] * factor
+            return full
+
+        rows = qkv.shape[0]
+        q = turned(normed(qkv[:, :heads * dim], q_weight).view(rows, heads, dim), key_freq, magnitude)
+        k = turned(normed(qkv[:, heads * dim:(heads + kv_heads) * dim], k_weight).view(rows, kv_heads, dim), key_freq,
+                   magnitude)
+        v = qkv[:, (heads + kv_heads) * dim:].view(rows, kv_heads, vdim)
+        if normalise_values:
+            v = v * torch.rsqrt((v * v).mean(-1, keepdim=True) + eps)
+        if value_freq is not None:
+            v = turned(v, value_freq, 1.0)
+        if write_kv:
+            page_size = k_pool.shape[2]
+            for t in range(rows):
+                slot = int(slots[t])
+                if slot < 0:
+                    continue
+                page, offset = divmod(slot, page_size)
+                k_pool[page, :, offset, :] = k[t].to(k_pool.dtype)
+                v_pool[page, :, offset, :] = v[t].to(v_pool.dtype)
+        return q.reshape(rows, heads * dim).to(k_pool.dtype)
+
+    def turn_heads(self, x, positions, freq, heads, dim, interleaved, sign=1.0):
+        turned = self._turn(x.float().view(-1, heads, dim), positions, freq * sign, interleaved)
+        x.copy_(turned.reshape(x.shape).to(x.dtype))
+        return x
+
+    def route_experts(self, x, router, correction, top, groups=1, keep=1, scoring="softmax", renormalise=False):
+        logits = x.float() @ router.T
+        scores = torch.softmax(logits, dim=-1) if scoring == "softmax" else torch.sigmoid(logits)
+        choice = scores if correction is None else scores + correction
+        experts = router.shape[0]
+        if keep < groups:
+            best = choice.view(-1, groups, experts // groups).max(dim=-1).values
+            kept = torch.zeros_like(best, dtype=torch.bool).scatter_(1, best.topk(keep, dim=-1).indices, True)
+            choice = choice.masked_fill(~kept.repeat_interleave(experts // groups, dim=1), float("-inf"))
+        chosen = choice.topk(top, dim=-1).indices
+        weights = scores.gather(1, chosen)
+        if renormalise:
+            weights = weights / weights.sum(-1, keepdim=True)
+        return chosen.to(torch.int32), weights
+
+    def routed_experts(self, x, chosen, weights, gate_up, down, block, activation="silu"):
+        out = torch.zeros((x.shape[0], down.shape[1]), dtype=torch.float32)
+        for row in range(x.shape[0]):
+            for t in range(chosen.shape[1]):
+                e = int(chosen[row, t])
+                hidden = self.gated_activation(self.linear(x[row:row + 1], gate_up[e]), block, activation)
+                out[row] += weights[row, t] * (hidden.float() @ down[e].float().T)[0]
         return out
