@@ -98,8 +98,14 @@ def attention(h, t, prefix, mixer, eps):
     return out.reshape(length, heads * vdim) @ t[prefix + "o"].T
 
 
-def route(h, t, prefix, router):
-    """Per token: the chosen experts (indices) and their weights."""
+CLOSE_CALL = 0.008
+
+
+def route(h, t, prefix, router, risk_out=None):
+    """Per token: the chosen experts (indices) and their weights.  ``risk_out`` (a list) receives, per
+    token, how much weight hangs on a close call: where the last chosen and the first left-out choice
+    score (or the last kept and the first dropped group) lie within CLOSE_CALL of each other, the
+    larger of the two experts' scores, else 0.  Tests of reduced precision leave such tokens out."""
     experts, top = router["experts"], router["top"]
     groups = router.get("groups") or {"count": 1, "keep": 1}
     count, keep = groups["count"], groups["keep"]
@@ -112,11 +118,23 @@ def route(h, t, prefix, router):
     allowed = allowed.repeat_interleave(size, dim=1)
     choice = torch.where(allowed, choice, torch.full_like(choice, -math.inf))
     chosen = choice.topk(top, dim=-1).indices
+    if risk_out is not None:
+        risk = torch.zeros(h.shape[0], dtype=h.dtype)
+        if top < experts:
+            ranked = choice.topk(top + 1, dim=-1)
+            close = (ranked.values[:, top - 1] - ranked.values[:, top]) < CLOSE_CALL
+            risk = torch.where(close, scores.gather(1, ranked.indices[:, top - 1:top + 1]).max(dim=-1).values, risk)
+        if keep < count:
+            ranked = best.topk(keep + 1, dim=-1)
+            close = (ranked.values[:, keep - 1] - ranked.values[:, keep]) < CLOSE_CALL
+            pair = scores.reshape(-1, count, size).max(dim=-1).values.gather(1, ranked.indices[:, keep - 1:keep + 1])
+            risk = torch.maximum(risk, torch.where(close, pair.max(dim=-1).values, torch.zeros_like(risk)))
+        risk_out.append(risk)
     return chosen, scores.gather(1, chosen)
 
 
-def experts(h, t, prefix, mlp):
-    chosen, weights = route(h, t, prefix, mlp["router"])
+def experts(h, t, prefix, mlp, risk_out=None):
+    chosen, weights = route(h, t, prefix, mlp["router"], risk_out)
     out = torch.zeros_like(h)
     for token in range(h.shape[0]):
         for e, w in zip(chosen[token].tolist(), weights[token]):
@@ -126,9 +144,9 @@ def experts(h, t, prefix, mlp):
     return out
 
 
-def forward(config, tensors, tokens, dtype=torch.float64, layers_out=None):
+def forward(config, tensors, tokens, dtype=torch.float64, layers_out=None, risk_out=None):
     """Logits [T, vocab] of one whole sequence; ``layers_out`` (a list) receives the stream after
-    every layer."""
+    every layer, ``risk_out`` (a list) one tensor per routed layer (see ``route``)."""
     t = {name: (value.to(dtype) if value.is_floating_point() else value) for name, value in tensors.items()}
     eps = float(config["norm"]["eps"])
     x = t["embed"][torch.as_tensor(tokens, dtype=torch.long)] * float(config["embedding"]["scale"])
@@ -139,7 +157,7 @@ def forward(config, tensors, tokens, dtype=torch.float64, layers_out=None):
         mixed = attention(layer_norm(x, t[p + "norm1"], eps), t, p + "mix.", layer["mixer"], eps)
         x = x + layer_norm(mixed, t[p + "norm1b"], eps)
         if layer.get("mlp") is not None:
-            passed = experts(layer_norm(x, t[p + "norm2"], eps), t, p + "mlp.", layer["mlp"])
+            passed = experts(layer_norm(x, t[p + "norm2"], eps), t, p + "mlp.", layer["mlp"], risk_out)
             x = x + layer_norm(passed, t[p + "norm2b"], eps)
         if layers_out is not None:
             layers_out.append(x.clone())
