@@ -191,6 +191,7 @@ class CudaOps:
         self.use_fused_norm = True
         self.use_tma_attention = True
         self.use_fused_rope = True
+        self.use_grouped_experts = True     # routed experts of many rows: sorted pairs through the grouped tcgen05 product
         self.use_cluster_merge = True       # chunks of a decode row merge through a cluster's shared memory
         self.split_prefill_items = True     # the tcgen05 prompt attention may cut long items into parts
         # MLR_TCGEN05_ATTENTION=0 in the environment keeps prompt attention on the mma.sync kernels
@@ -467,6 +468,7 @@ class CudaOps:
     # Rows up to which the few-rows kernel is chosen.  It accepts up to 64, but measured on the
     # 0.5B layer sizes it loses to the tcgen05 kernel at 64 rows (3.72 against 3.23 ms per step).
     SKINNY_ROWS = 16
+    GROUPED_EXPERT_ROWS = 16          # rows up to which every (row, expert) pair of a routed feed-forward streams its expert alone
     SKINNY_ROWS_SMALL_WEIGHT = 32     # rows up to which matrices of at most SKINNY_SMALL_WEIGHT elements stay with it
     SKINNY_SMALL_WEIGHT = 2 << 20
     SKINNY_LARGE_WEIGHT = 32 << 20    # elements from which more than SKINNY_LARGE_WEIGHT_ROWS rows go to the tcgen05 kernel
@@ -1353,11 +1355,50 @@ class CudaOps:
         if rows == 0:
             return out
         lib = build.load_library("routed_experts")
-        hidden = torch.empty((rows * top, inner), dtype=x.dtype, device=x.device)
-        _check(lib.mlr_expert_hidden(_ptr(x), _ptr(chosen), _ptr(gate_up), _ptr(hidden), rows, K, inner, top, int(block),
-                                     act, _code(x.dtype), _stream()), "expert_hidden")
-        _check(lib.mlr_expert_down(_ptr(hidden), _ptr(chosen), _ptr(weights), _ptr(down), _ptr(out), rows, N, inner,
-                                   top, _code(x.dtype), _stream()), "expert_down")
+        pairs = rows * top
+        grouped = (self.use_tensor_cores and self.use_grouped_experts and x.dtype == torch.bfloat16
+                   and rows > self.GROUPED_EXPERT_ROWS and K % 8 == 0 and inner % 8 == 0
+                   and x.data_ptr() % 16 == 0 and gate_up.data_ptr() % 16 == 0 and down.data_ptr() % 16 == 0)
+        if not grouped:
+            # every (row, chosen expert) pair streams its expert's matrices
+            hidden = torch.empty((pairs, inner), dtype=x.dtype, device=x.device)
+            _check(lib.mlr_expert_hidden(_ptr(x), _ptr(chosen), _ptr(gate_up), _ptr(hidden), rows, K, inner, top,
+                                         int(block), act, _code(x.dtype), _stream()), "expert_hidden")
+            _check(lib.mlr_expert_down(_ptr(hidden), _ptr(chosen), _ptr(weights), _ptr(down), _ptr(out), rows, N, inner,
+                                       top, _code(x.dtype), _stream()), "expert_down")
+            return out
+        # many rows: the pairs sorted by expert, each expert's rows through the tensor-core product with
+        # its own matrices (tiles of 128 rows of one expert), the results summed per row in the order
+        # of the row's choices
+        tile_rows = 128
+        max_tiles = min(pairs, -(-pairs // tile_rows) + experts)
+        place = torch.empty(pairs, dtype=torch.int32, device=x.device)
+        token_of = torch.empty(pairs, dtype=torch.int32, device=x.device)
+        tiles = torch.empty(max_tiles * 3, dtype=torch.int32, device=x.device)
+        _check(lib.mlr_sort_pairs(_ptr(chosen), _ptr(place), _ptr(token_of), _ptr(tiles), pairs, top, experts,
+                                  tile_rows, max_tiles, _stream()), "sort_pairs")
+        sorted_x = torch.empty((pairs, K), dtype=x.dtype, device=x.device)
+        _check(lib.mlr_gather_rows_by(_ptr(x), _ptr(token_of), _ptr(sorted_x), pairs, K * x.element_size(),
+                                      _stream()), "gather_rows_by")
+        gemm = build.load_library("gemm_tcgen05")
+        error_word = _ptr(self._workspace(x.device)["error_word"])
+        fused = self.use_fused_swiglu and block == self.SWIGLU_BLOCK and (2 * inner) % 128 == 0
+        if fused:
+            hidden = torch.empty((pairs, inner), dtype=x.dtype, device=x.device)
+            _check(gemm.mlr_gemm_tcgen05_grouped(_ptr(sorted_x), _ptr(gate_up), _ptr(hidden), _ptr(tiles), max_tiles,
+                                                 pairs, experts, 2 * inner, K, 0, 1 + act, error_word, _stream()),
+                   "grouped gate/up product")
+        else:
+            both = torch.empty((pairs, 2 * inner), dtype=x.dtype, device=x.device)
+            _check(gemm.mlr_gemm_tcgen05_grouped(_ptr(sorted_x), _ptr(gate_up), _ptr(both), _ptr(tiles), max_tiles,
+                                                 pairs, experts, 2 * inner, K, 0, 0, error_word, _stream()),
+                   "grouped gate/up product")
+            hidden = self.gated_activation(both, block, activation)
+        y = torch.empty((pairs, N), dtype=torch.float32, device=x.device)
+        _check(gemm.mlr_gemm_tcgen05_grouped(_ptr(hidden), _ptr(down), _ptr(y), _ptr(tiles), max_tiles, pairs, experts,
+                                             N, inner, 1, 0, error_word, _stream()), "grouped down product")
+        _check(lib.mlr_combine_pairs(_ptr(y), _ptr(place), _ptr(weights), _ptr(out), rows, N, top, _stream()),
+               "combine_pairs")
         return out
 
     def sample(self, logits: torch.Tensor, temperatures: torch.Tensor, seeds: torch.Tensor,

@@ -98,7 +98,7 @@ def attention(h, t, prefix, mixer, eps):
     return out.reshape(length, heads * vdim) @ t[prefix + "o"].T
 
 
-CLOSE_CALL = 0.008
+CLOSE_CALL = 0.02
 
 
 def route(h, t, prefix, router, risk_out=None):
