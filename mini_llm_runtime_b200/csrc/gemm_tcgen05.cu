@@ -582,10 +582,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
 
 
 // ---------------------------------------------------------------- host side
+// Dynamic shared memory an instantiation may be launched with: raised when a launch needs more, and
+// remembered per instantiation (every launcher of that instantiation asks here).
 template <int BN, bool SWAP, bool SWIGLU, int BM = TILE_ROWS>
-static int launch(const void* x, const void* w, const GemmParams& p, int splits, cudaStream_t stream) {
-  const size_t shared = (size_t)p.stages * (BM * TILE_K * 2 + BN * TILE_K * 2) + 1024;
-  if (BM != TILE_ROWS && splits != 1) return MLR_BAD_SIZE;
+static int allow_shared(size_t shared) {
   static size_t configured = 0;
   if (shared > configured) {
     cudaError_t err = cudaFuncSetAttribute(gemm_tcgen05_kernel<BN, SWAP, SWIGLU, BM>,
@@ -593,6 +593,14 @@ static int launch(const void* x, const void* w, const GemmParams& p, int splits,
     if (err != cudaSuccess) return (int)err;
     configured = shared;
   }
+  return 0;
+}
+
+template <int BN, bool SWAP, bool SWIGLU, int BM = TILE_ROWS>
+static int launch(const void* x, const void* w, const GemmParams& p, int splits, cudaStream_t stream) {
+  const size_t shared = (size_t)p.stages * (BM * TILE_K * 2 + BN * TILE_K * 2) + 1024;
+  if (BM != TILE_ROWS && splits != 1) return MLR_BAD_SIZE;
+  if (int err = allow_shared<BN, SWAP, SWIGLU, BM>(shared)) return err;
   const void* a_base = SWAP ? w : x;
   const void* b_base = SWAP ? x : w;
   const int a_rows = SWAP ? p.N : p.M, b_rows = SWAP ? p.M : p.N;
@@ -853,13 +861,7 @@ template <int BN, bool SWIGLU>
 static int launch_grouped(const void* x, const void* w, const GemmParams& p, int rows, int groups, int max_tiles,
                           cudaStream_t stream) {
   const size_t shared = (size_t)p.stages * (TILE_ROWS * TILE_K * 2 + BN * TILE_K * 2) + 1024;
-  static size_t configured = 0;
-  if (shared > configured) {
-    cudaError_t err = cudaFuncSetAttribute(gemm_tcgen05_kernel<BN, false, SWIGLU, TILE_ROWS>,
-                                           cudaFuncAttributeMaxDynamicSharedMemorySize, (int)shared);
-    if (err != cudaSuccess) return (int)err;
-    configured = shared;
-  }
+  if (int err = allow_shared<BN, false, SWIGLU, TILE_ROWS>(shared)) return err;
   CUtensorMap map_a, map_b;
   if (!cached_tile_map(&map_a, x, rows, p.K, TILE_ROWS) || !cached_tile_map(&map_b, w, groups * p.N, p.K, BN))
     return MLR_BAD_ALIGNMENT;

@@ -104,6 +104,28 @@ def test_expert_kernels_against_their_formula(rows, width, inner, experts, top, 
     assert error < (1e-5 if dtype == F32 else 1.5e-2), error
 
 
+def test_grouped_and_plain_products_share_a_kernel_without_harm():
+    """The grouped product and the plain product of many rows are launches of one kernel with rings
+    of different depths; each keeps working after the other has run."""
+    from mini_llm_runtime_b200 import ops
+    k = ops.current()
+    generator = torch.Generator().manual_seed(3)
+    x = torch.randn(300, 1024, generator=generator).to(BF16).to(DEVICE)
+    w = (torch.randn(1024, 1024, generator=generator) * 0.03).to(BF16).to(DEVICE)
+    want = x.float() @ w.float().T
+    small = torch.randn(300, 64, generator=generator).to(BF16).to(DEVICE)
+    gate_up = (torch.randn(4, 256, 64, generator=generator) * 0.1).to(BF16).to(DEVICE)
+    down = (torch.randn(4, 64, 128, generator=generator) * 0.1).to(BF16).to(DEVICE)
+    chosen = torch.randint(0, 4, (300, 1), generator=generator, dtype=torch.int32).to(DEVICE)
+    weights = torch.ones(300, 1, device=DEVICE)
+    for _ in range(2):
+        got = k.linear(x, w, out_dtype=F32)
+        assert float((got - want).abs().max()) < 2e-2 * float(want.abs().max())
+        assert torch.isfinite(k.routed_experts(small, chosen, weights, gate_up, down, 64)).all()
+    torch.cuda.synchronize()
+    k.raise_if_device_error()
+
+
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("heads,kv_heads,dim,vdim,rot,interleaved", [(6, 2, 16, 24, 16, True), (3, 3, 10, 6, 6, True),
                                                                       (4, 1, 64, 64, 32, False), (2, 2, 128, 64, 128, True)])
