@@ -554,6 +554,15 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
             uint4* dst = reinterpret_cast<uint4*>(out_bf16 + (size_t)m * p.N + n0);
             dst[0] = make_uint4(packed[0], packed[1], packed[2], packed[3]);
             dst[1] = make_uint4(packed[4], packed[5], packed[6], packed[7]);
+          } else if (p.out_f32 && (p.N & 3) == 0 && n0 + 16 <= p.N) {
+            float4* dst = reinterpret_cast<float4*>(out_f32 + (size_t)m * p.N + n0);
+#pragma unroll
+            for (int c = 0; c < 16; c += 4) {
+              float b[4];
+#pragma unroll
+              for (int i = 0; i < 4; ++i) b[i] = p.bias != nullptr ? to_float(p.bias[n0 + c + i]) : 0.f;
+              dst[c >> 2] = make_float4(v[q + c] + b[0], v[q + c + 1] + b[1], v[q + c + 2] + b[2], v[q + c + 3] + b[3]);
+            }
           } else {
 #pragma unroll
             for (int c = 0; c < 16; ++c) {

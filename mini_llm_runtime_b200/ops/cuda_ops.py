@@ -1326,8 +1326,9 @@ class CudaOps:
             raise KernelError(f"unknown router scoring {scoring!r}")
         chosen = torch.empty((x.shape[0], top), dtype=torch.int32, device=x.device)
         weights = torch.empty((x.shape[0], top), dtype=torch.float32, device=x.device)
+        logits = torch.empty((x.shape[0], experts), dtype=torch.float32, device=x.device)
         _check(build.load_library("routed_experts").mlr_route_experts(
-            _ptr(x), _ptr(router), _ptr(correction), _ptr(chosen), _ptr(weights), x.shape[0], x.shape[1], experts,
+            _ptr(x), _ptr(router), _ptr(correction), _ptr(logits), _ptr(chosen), _ptr(weights), x.shape[0], x.shape[1], experts,
             int(top), int(groups), int(keep), int(scoring == "sigmoid"), int(bool(renormalise)), _code(x.dtype),
             _stream()), "route_experts")
         return chosen, weights
