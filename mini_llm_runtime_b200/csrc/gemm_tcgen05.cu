@@ -134,7 +134,7 @@ struct GemmParams {
   float* scratch;           // [tiles][splits][BN][128] partial tiles (splits > 1)
   int* counters;            // one per output tile, zero between launches
   int* error_word;
-  // Grouped form (many rows, no split-K): blockIdx.x indexes this list of (group, first row, end row)
+  // Grouped form (many rows, no split-K): blockIdx.y indexes this list of (group, first row, end row)
   // instead of a 128-row tile of x; the tile's weight rows are those of its group, N rows each, in
   // the stacked matrix [groups * N, K]; rows at or beyond the end row are computed and not written;
   // an entry whose group is negative is unused.  The list is device memory written by an earlier kernel.
@@ -310,13 +310,18 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int stages = p.stages;
-  int a_row0 = blockIdx.x * BM;                // first row of the 128-row (or 256-row) operand
-  const int n_tile0 = blockIdx.y * BN;         // first row of the BN-row operand within its matrix
+  // grouped form: the grid is (column tiles, row tiles), so that the CTAs that share a row tile's
+  // activations run together; every weight tile of a group is read by one CTA per row tile anyway
+  const bool grouped = !SWAP && !PAIR && p.group_tiles != nullptr;
+  const int tile_x = grouped ? blockIdx.y : blockIdx.x;
+  const int tile_y = grouped ? blockIdx.x : blockIdx.y;
+  int a_row0 = tile_x * BM;                    // first row of the 128-row (or 256-row) operand
+  const int n_tile0 = tile_y * BN;             // first row of the BN-row operand within its matrix
   int b_row0 = n_tile0;
   int row_limit = p.M;
-  if (!SWAP && !PAIR && BM == TILE_ROWS && p.group_tiles != nullptr) {
+  if (grouped) {
     pdl_wait();                                // the list comes from an earlier kernel
-    const int* entry = p.group_tiles + 3 * blockIdx.x;
+    const int* entry = p.group_tiles + 3 * tile_x;
     const int group = __ldcg(entry);
     if (group < 0) return;                     // the whole CTA, before any barrier or tensor memory
     a_row0 = __ldcg(entry + 1);
@@ -498,7 +503,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
           if (m >= row_limit) continue;
 #pragma unroll
           for (int q = 0; q < 32; q += 16) {
-            const int n0 = (blockIdx.y * (BN / 128) + block) * 64 + c0 + q;
+            const int n0 = (tile_y * (BN / 128) + block) * 64 + c0 + q;
             uint32_t packed[8];
 #pragma unroll
             for (int c = 0; c < 16; c += 2) {
@@ -866,16 +871,17 @@ MLR_EXPORT int mlr_gemm_tcgen05(const void* x, const void* w, const void* bias, 
 
 // ---------------------------------------------------------------- grouped form
 namespace mlr {
-template <int BN, bool SWIGLU>
+template <int BN, bool SWIGLU, int BM = TILE_ROWS>
 static int launch_grouped(const void* x, const void* w, const GemmParams& p, int rows, int groups, int max_tiles,
                           cudaStream_t stream) {
-  const size_t shared = (size_t)p.stages * (TILE_ROWS * TILE_K * 2 + BN * TILE_K * 2) + 1024;
-  if (int err = allow_shared<BN, false, SWIGLU, TILE_ROWS>(shared)) return err;
+  const size_t shared = (size_t)p.stages * (BM * TILE_K * 2 + BN * TILE_K * 2) + 1024;
+  if (int err = allow_shared<BN, false, SWIGLU, BM>(shared)) return err;
   CUtensorMap map_a, map_b;
   if (!cached_tile_map(&map_a, x, rows, p.K, TILE_ROWS) || !cached_tile_map(&map_b, w, groups * p.N, p.K, BN))
     return MLR_BAD_ALIGNMENT;
-  dim3 grid(max_tiles, (p.N + BN - 1) / BN, 1);
-  launch_kernel(gemm_tcgen05_kernel<BN, false, SWIGLU, TILE_ROWS>, dim3(grid), dim3(GEMM_THREADS), shared, stream, map_a,
+  if (max_tiles > 65535) return MLR_TOO_LARGE;
+  dim3 grid((p.N + BN - 1) / BN, max_tiles, 1);
+  launch_kernel(gemm_tcgen05_kernel<BN, false, SWIGLU, BM>, dim3(grid), dim3(GEMM_THREADS), shared, stream, map_a,
                 map_b, p);
   return launch_status();
 }
@@ -883,14 +889,15 @@ static int launch_grouped(const void* x, const void* w, const GemmParams& p, int
 
 // The product of rows that are sorted by group with each group's own matrix: x [rows, K], w [groups, N, K]
 // (stacked), out [rows, N] (or [rows, N/2] bfloat16 with swiglu, as in mlr_gemm_tcgen05).  `tiles` is
-// device memory, int32 [max_tiles][3] = (group, first row, end row) per tile of up to 128 rows of one
-// group, group < 0 for unused entries; it may be written by the kernel just before this one.  A
-// 128-row load may run into the next group's rows (or past the last row: zeros); those rows are
-// computed and dropped.  N % BN need not hold only without swiglu: a weight tile that would run into
+// device memory, int32 [max_tiles][3] = (group, first row, end row) per tile of up to `tile_rows` (128,
+// or 256 where N is a multiple of 256: two accumulators from one load of the weight tile, one CTA
+// per SM) rows of one group, group < 0 for unused entries; it may be written by the kernel just
+// before this one.  A 128-row load may run into the next group's rows (or past the last row: zeros);
+// those rows are computed and dropped.  N % BN need not hold only without swiglu: a weight tile that would run into
 // the next group's rows is loaded but its columns beyond N are never written.
 MLR_EXPORT int mlr_gemm_tcgen05_grouped(const void* x, const void* w, void* out, const int* tiles, int max_tiles, int rows,
-                                        int groups, int N, int K, int out_f32, int swiglu, int* error_word,
-                                        cudaStream_t stream) {
+                                        int groups, int N, int K, int out_f32, int swiglu, int tile_rows,
+                                        int* error_word, cudaStream_t stream) {
   if (rows == 0 || max_tiles == 0) return MLR_OK;
   if (rows < 0 || max_tiles < 0 || groups <= 0 || N <= 0 || K <= 0 || tiles == nullptr) return MLR_BAD_SIZE;
   if (K % 8 != 0 || ((uintptr_t)x & 15) || ((uintptr_t)w & 15)) return MLR_BAD_ALIGNMENT;
@@ -898,14 +905,17 @@ MLR_EXPORT int mlr_gemm_tcgen05_grouped(const void* x, const void* w, void* out,
   if ((long long)groups * N > 0x7fffffffll) return MLR_TOO_LARGE;
   const int total_kb = (K + TILE_K - 1) / TILE_K;
   const bool wide = N % 256 == 0 && N >= 512;
+  const bool tall = tile_rows == 2 * TILE_ROWS;
+  if ((tile_rows != TILE_ROWS && !tall) || (tall && !wide)) return MLR_BAD_SIZE;
   GemmParams p;
   p.M = rows; p.N = N; p.K = K;
   p.k_blocks_per_split = total_kb;
   p.splits = 1;
-  // rings of 32 KB (128 x 128) or 48 KB (128 x 256) stages, as deep as K is long, within 96 KB so that
-  // two CTAs share an SM and one's epilogue runs under the other's main loop
+  // tall tiles: rings of up to three 64 KB stages, one CTA per SM.  Else rings of 32 KB (128 x 128) or
+  // 48 KB (128 x 256) stages, as deep as K is long, within 96 KB so that two CTAs share an SM and one's
+  // epilogue runs under the other's main loop
   const int stage_bytes = TILE_ROWS * TILE_K * 2 + (wide ? 256 : 128) * TILE_K * 2;
-  int stages = 96 * 1024 / stage_bytes;
+  int stages = tall ? 3 : 96 * 1024 / stage_bytes;
   if (stages > total_kb) stages = total_kb;
   p.stages = stages < 2 ? 2 : stages;
   p.bias = nullptr;
@@ -918,6 +928,8 @@ MLR_EXPORT int mlr_gemm_tcgen05_grouped(const void* x, const void* w, void* out,
   p.counters = nullptr;
   p.error_word = error_word;
   p.group_tiles = tiles;
+  if (tall) return swiglu ? launch_grouped<256, true, 2 * TILE_ROWS>(x, w, p, rows, groups, max_tiles, stream)
+                          : launch_grouped<256, false, 2 * TILE_ROWS>(x, w, p, rows, groups, max_tiles, stream);
   if (swiglu) return wide ? launch_grouped<256, true>(x, w, p, rows, groups, max_tiles, stream)
                           : launch_grouped<128, true>(x, w, p, rows, groups, max_tiles, stream);
   return wide ? launch_grouped<256, false>(x, w, p, rows, groups, max_tiles, stream)

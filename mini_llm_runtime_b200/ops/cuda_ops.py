@@ -192,6 +192,7 @@ class CudaOps:
         self.use_tma_attention = True
         self.use_fused_rope = True
         self.use_grouped_experts = True     # routed experts of many rows: sorted pairs through the grouped tcgen05 product
+        self.use_tall_expert_tiles = False  # .. in tiles of 256 rows of an expert where experts get more than 128 rows (measured: no gain)
         self.use_cluster_merge = True       # chunks of a decode row merge through a cluster's shared memory
         self.split_prefill_items = True     # the tcgen05 prompt attention may cut long items into parts
         # MLR_TCGEN05_ATTENTION=0 in the environment keeps prompt attention on the mma.sync kernels
@@ -1371,7 +1372,10 @@ class CudaOps:
         # many rows: the pairs sorted by expert, each expert's rows through the tensor-core product with
         # its own matrices (tiles of 128 rows of one expert), the results summed per row in the order
         # of the row's choices
-        tile_rows = 128
+        # rows of a tile: 256 (two accumulators from one load of an expert's weight tile) when an expert
+        # gets more than 128 rows on average and both products have the columns for it, else 128
+        both_wide = all(n % 256 == 0 and n >= 512 for n in (2 * inner, N))
+        tile_rows = 256 if self.use_tall_expert_tiles and both_wide and pairs > 128 * experts else 128
         max_tiles = min(pairs, -(-pairs // tile_rows) + experts)
         place = torch.empty(pairs, dtype=torch.int32, device=x.device)
         token_of = torch.empty(pairs, dtype=torch.int32, device=x.device)
@@ -1387,17 +1391,17 @@ class CudaOps:
         if fused:
             hidden = torch.empty((pairs, inner), dtype=x.dtype, device=x.device)
             _check(gemm.mlr_gemm_tcgen05_grouped(_ptr(sorted_x), _ptr(gate_up), _ptr(hidden), _ptr(tiles), max_tiles,
-                                                 pairs, experts, 2 * inner, K, 0, 1 + act, error_word, _stream()),
+                                                 pairs, experts, 2 * inner, K, 0, 1 + act, tile_rows, error_word, _stream()),
                    "grouped gate/up product")
         else:
             both = torch.empty((pairs, 2 * inner), dtype=x.dtype, device=x.device)
             _check(gemm.mlr_gemm_tcgen05_grouped(_ptr(sorted_x), _ptr(gate_up), _ptr(both), _ptr(tiles), max_tiles,
-                                                 pairs, experts, 2 * inner, K, 0, 0, error_word, _stream()),
+                                                 pairs, experts, 2 * inner, K, 0, 0, tile_rows, error_word, _stream()),
                    "grouped gate/up product")
             hidden = self.gated_activation(both, block, activation)
         y = torch.empty((pairs, N), dtype=torch.float32, device=x.device)
         _check(gemm.mlr_gemm_tcgen05_grouped(_ptr(hidden), _ptr(down), _ptr(y), _ptr(tiles), max_tiles, pairs, experts,
-                                             N, inner, 1, 0, error_word, _stream()), "grouped down product")
+                                             N, inner, 1, 0, tile_rows, error_word, _stream()), "grouped down product")
         _check(lib.mlr_combine_pairs(_ptr(y), _ptr(place), _ptr(weights), _ptr(out), rows, N, top, _stream()),
                "combine_pairs")
         return out

@@ -71,10 +71,12 @@ def test_router_kernel_against_its_formula():
 
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("rows,width,inner,experts,top", [(1, 40, 24, 3, 2), (5, 72, 52, 5, 1), (150, 64, 64, 4, 3),
-                                                            (300, 128, 192, 8, 2), (700, 256, 128, 16, 4), (20, 36, 20, 2, 2)])
+                                                            (300, 128, 192, 8, 2), (700, 256, 128, 16, 4), (20, 36, 20, 2, 2),
+                                                            (700, 512, 256, 4, 2), (900, 768, 384, 5, 3)])
 def test_expert_kernels_against_their_formula(rows, width, inner, experts, top, dtype):
-    """Few and many rows (the sorted, grouped tensor-core product takes the latter in bfloat16), sizes
-    with and without the interleaved gate/up blocks, experts that get no row at all."""
+    """Few and many rows (the sorted, grouped tensor-core product takes the latter in bfloat16: in tiles
+    of 128 rows of an expert, or of 256 where the products are wide and the experts get many rows),
+    sizes with and without the interleaved gate/up blocks, experts that get no row at all."""
     from mini_llm_runtime_b200 import ops
     from mini_llm_runtime_b200.config import PartSpec
     from mini_llm_runtime_b200.parts import build_part
@@ -87,8 +89,14 @@ def test_expert_kernels_against_their_formula(rows, width, inner, experts, top, 
     pool = experts - 1 if experts > top else experts      # where there is room, the last expert stays idle
     chosen = torch.stack([torch.randperm(pool, generator=generator)[:top] for _ in range(rows)]).to(torch.int32)
     weights = torch.rand(rows, top, generator=generator)
-    got = ops.current().routed_experts(x.to(DEVICE).to(dtype), chosen.to(DEVICE), weights.to(DEVICE), part.w_gate_up,
-                                       part.w_down, part.block)
+    kernels = ops.current()
+    before = kernels.use_tall_expert_tiles
+    kernels.use_tall_expert_tiles = rows == 900          # one of the wide cases in tiles of 256 rows
+    try:
+        got = kernels.routed_experts(x.to(DEVICE).to(dtype), chosen.to(DEVICE), weights.to(DEVICE), part.w_gate_up,
+                                     part.w_down, part.block)
+    finally:
+        kernels.use_tall_expert_tiles = before
     want = torch.zeros(rows, width, dtype=torch.float64)
     x64 = x.double()
     for e in range(experts):
