@@ -21,6 +21,7 @@ SIZES = {
     # width, heads, experts, chosen experts, an expert's inner width, groups (count, kept), layers, vocabulary
     "896": dict(width=896, layers=12, vocab=32000, heads=14, kv_heads=2, dim=64, experts=16, top=2, ff=2432, groups=(4, 2)),
     "2048": dict(width=2048, layers=12, vocab=32000, heads=16, kv_heads=4, dim=128, experts=64, top=6, ff=1408, groups=(8, 4)),
+    "4096": dict(width=4096, layers=8, vocab=32000, heads=32, kv_heads=8, dim=128, experts=32, top=4, ff=2048, groups=(4, 2)),
 }
 
 
@@ -67,6 +68,15 @@ def bopilorn_numbers(size, batch=8):
             "kv_bytes_per_token": 2 * layers * s["kv_heads"] * s["dim"] * 2,
             "linear_flops_per_token": 2 * layers * active, "head_flops_per_row": 2 * head,
             "attention_flops": lambda rows, before=0: layers * 4 * s["heads"] * s["dim"] * (rows * before + rows * (rows + 1) // 2)}
+
+
+def prefill_weight_bytes(size):
+    """Bytes of weights a prefill of 2,048 rows reads: every expert of every layer once."""
+    s = SIZES[size]
+    width = s["width"]
+    attention = (s["heads"] + 2 * s["kv_heads"]) * s["dim"] * width + width * s["heads"] * s["dim"]
+    return int(2 * (s["layers"] * (attention + 2 * s["experts"] * width + s["experts"] * 3 * width * s["ff"])
+                    + s["vocab"] * width))
 
 
 def kernel_points(size, peak):
@@ -204,6 +214,13 @@ def run(args, host):
                 bench = Bench(f"{name} {size}", config, numbers, host)
                 entry[name] = model_points(bench, host, args, peak)
                 entry[name]["layers"] = len(bench.model.blocks)
+                # the prefill's roofline: the slower of its flops at the measured peak and the bytes it
+                # must read (every weight once: 2,048 rows touch every expert) at the measured bandwidth
+                flops = entry[name]["prefill_frac_of_bf16_peak"] * peak["bf16_tflops"] * 1e12 * entry[name]["prefill_2048_ms"] / 1e3
+                weights = prefill_weight_bytes(size) if name == "bopilorn" else numbers["weight_bytes"]
+                bound_ms = max(flops / (peak["bf16_tflops"] * 1e12), weights / (peak["hbm_gbs"] * 1e9)) * 1e3
+                entry[name]["prefill_roofline_ms"] = round(bound_ms, 3)
+                entry[name]["prefill_frac_of_roofline"] = round(bound_ms / entry[name]["prefill_2048_ms"], 4)
                 bench.close()
             record["sizes"][size] = entry
             record["kernels"][size] = kernel_points(size, peak)

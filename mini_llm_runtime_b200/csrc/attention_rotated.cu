@@ -30,7 +30,7 @@ __device__ __forceinline__ void pair_places(int i, int n, int interleaved, int* 
 }
 
 template <typename T>
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(1024)
 rotated_prepare_kernel(const float* qkv, const int* positions, const float* __restrict__ q_weight,
                        const float* __restrict__ k_weight, const float* __restrict__ key_freq,
                        const float* __restrict__ value_freq, const long long* slots, T* __restrict__ q_out, T* k_pool,
@@ -202,12 +202,15 @@ MLR_EXPORT int mlr_rotated_prepare(const float* qkv, const int* positions, const
     return MLR_BAD_SIZE;
   const size_t shared = sizeof(float) * ((size_t)(heads + kv_heads) * dim + (size_t)kv_heads * vdim + 32 + kv_heads);
   if (shared > 200 * 1024) return MLR_TOO_LARGE;
+  // threads by the row's width alone (the sums' order follows the block's size: a row must not see the batch)
+  const int row_width = (heads + kv_heads) * dim + kv_heads * vdim;
+  const int threads = row_width <= 2048 ? 256 : row_width <= 4096 ? 512 : 1024;
   auto launch = [&](auto kernel, auto* q_typed, auto* k_typed, auto* v_typed) -> int {
     if (shared > 48 * 1024) {
       cudaError_t err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)shared);
       if (err != cudaSuccess) return (int)err;
     }
-    launch_kernel(kernel, dim3(rows), dim3(256), shared, stream, qkv, positions, q_weight, k_weight, key_freq, value_freq,
+    launch_kernel(kernel, dim3(rows), dim3(threads), shared, stream, qkv, positions, q_weight, k_weight, key_freq, value_freq,
                   slots, q_typed, k_typed, v_typed, heads, kv_heads, dim, vdim, rot, interleaved, normalise_values, eps,
                   magnitude, page_size, write_kv);
     return launch_status();

@@ -184,24 +184,29 @@ layer_norm_step_warp_kernel(float* x, const float* delta, const float* __restric
   }
 }
 
-// Steps of few rows (decoding): one CTA of 128 threads per row, at most four float4 pieces per thread,
-// and every operand (the row, what is added, the norms' vectors) asked for before the first is used, so
-// that the pass costs one trip to memory instead of one per phase.
-__device__ __forceinline__ float block_sum_128(float v, float* scratch) {
+// Steps of few rows (decoding): one CTA of THREADS threads (128, or more for rows wider than 2,048)
+// per row, at most four float4 pieces per thread, and every operand (the row, what is added, the
+// norms' vectors) asked for before the first is used, so that the pass costs one trip to memory
+// instead of one per phase.
+template <int THREADS>
+__device__ __forceinline__ float block_sum_of(float v, float* scratch) {
   v = warp_sum(v);
   __syncthreads();
   if ((threadIdx.x & 31) == 0) scratch[threadIdx.x >> 5] = v;
   __syncthreads();
-  return (scratch[0] + scratch[1]) + (scratch[2] + scratch[3]);
+  float total = (scratch[0] + scratch[1]) + (scratch[2] + scratch[3]);
+#pragma unroll
+  for (int i = 4; i < THREADS / 32; i += 4) total += (scratch[i] + scratch[i + 1]) + (scratch[i + 2] + scratch[i + 3]);
+  return total;
 }
 
-template <typename T>
-__global__ void __launch_bounds__(128)
+template <typename T, int THREADS>
+__global__ void __launch_bounds__(THREADS)
 layer_norm_step_row_kernel(float* x, const float* delta, const float* __restrict__ dw, const float* __restrict__ db,
                            const float* __restrict__ offset, const float* __restrict__ w, const float* __restrict__ b,
                            T* __restrict__ out, int width, float eps) {
   pdl_trigger();
-  __shared__ float scratch[4];
+  __shared__ float scratch[THREADS / 32];
   constexpr int CH = 4;
   const int pieces = width >> 2;
   const size_t base = (size_t)blockIdx.x * width;
@@ -209,7 +214,7 @@ layer_norm_step_row_kernel(float* x, const float* delta, const float* __restrict
   float4 dwv[CH], dbv[CH], ov[CH], wv[CH], bv[CH], dv[CH], xv[CH];
 #pragma unroll
   for (int j = 0; j < CH; ++j) {
-    const int c = threadIdx.x + 128 * j;
+    const int c = threadIdx.x + THREADS * j;
     const bool in = c < pieces;
     dwv[j] = in && delta != nullptr ? reinterpret_cast<const float4*>(dw)[c] : zero;
     dbv[j] = in && delta != nullptr ? reinterpret_cast<const float4*>(db)[c] : zero;
@@ -220,7 +225,7 @@ layer_norm_step_row_kernel(float* x, const float* delta, const float* __restrict
   pdl_wait();
 #pragma unroll
   for (int j = 0; j < CH; ++j) {
-    const int c = threadIdx.x + 128 * j;
+    const int c = threadIdx.x + THREADS * j;
     const bool in = c < pieces;
     dv[j] = in && delta != nullptr ? __ldcg(reinterpret_cast<const float4*>(delta + base) + c) : zero;
     xv[j] = in ? __ldcg(reinterpret_cast<const float4*>(x + base) + c) : zero;
@@ -229,15 +234,15 @@ layer_norm_step_row_kernel(float* x, const float* delta, const float* __restrict
     float sum = 0.f;
 #pragma unroll
     for (int j = 0; j < CH; ++j) sum += (dv[j].x + dv[j].y) + (dv[j].z + dv[j].w);      // pieces past the row are zeros
-    const float mean = block_sum_128(sum, scratch) / (float)width;
+    const float mean = block_sum_of<THREADS>(sum, scratch) / (float)width;
     float sq = 0.f;
 #pragma unroll
     for (int j = 0; j < CH; ++j)
-      if (threadIdx.x + 128 * j < pieces) {
+      if (threadIdx.x + THREADS * j < pieces) {
         const float a = dv[j].x - mean, bb = dv[j].y - mean, c = dv[j].z - mean, d = dv[j].w - mean;
         sq += fmaf(a, a, bb * bb) + fmaf(c, c, d * d);
       }
-    const float rstd = 1.f / sqrtf(block_sum_128(sq, scratch) / (float)width + eps);
+    const float rstd = 1.f / sqrtf(block_sum_of<THREADS>(sq, scratch) / (float)width + eps);
 #pragma unroll
     for (int j = 0; j < CH; ++j) {
       const float4 add = normalised(dv[j], mean, rstd, dwv[j], dbv[j]);
@@ -251,26 +256,26 @@ layer_norm_step_row_kernel(float* x, const float* delta, const float* __restrict
   if (delta != nullptr || offset != nullptr) {
 #pragma unroll
     for (int j = 0; j < CH; ++j)
-      if (threadIdx.x + 128 * j < pieces) store4(x + base + 4 * (threadIdx.x + 128 * j), xv[j]);
+      if (threadIdx.x + THREADS * j < pieces) store4(x + base + 4 * (threadIdx.x + THREADS * j), xv[j]);
   }
   if (out == nullptr) return;
   float sum = 0.f;
 #pragma unroll
   for (int j = 0; j < CH; ++j)
-    if (threadIdx.x + 128 * j < pieces) sum += (xv[j].x + xv[j].y) + (xv[j].z + xv[j].w);
-  const float mean = block_sum_128(sum, scratch) / (float)width;
+    if (threadIdx.x + THREADS * j < pieces) sum += (xv[j].x + xv[j].y) + (xv[j].z + xv[j].w);
+  const float mean = block_sum_of<THREADS>(sum, scratch) / (float)width;
   float sq = 0.f;
 #pragma unroll
   for (int j = 0; j < CH; ++j)
-    if (threadIdx.x + 128 * j < pieces) {
+    if (threadIdx.x + THREADS * j < pieces) {
       const float a = xv[j].x - mean, bb = xv[j].y - mean, c = xv[j].z - mean, d = xv[j].w - mean;
       sq += fmaf(a, a, bb * bb) + fmaf(c, c, d * d);
     }
-  const float rstd = 1.f / sqrtf(block_sum_128(sq, scratch) / (float)width + eps);
+  const float rstd = 1.f / sqrtf(block_sum_of<THREADS>(sq, scratch) / (float)width + eps);
 #pragma unroll
   for (int j = 0; j < CH; ++j)
-    if (threadIdx.x + 128 * j < pieces)
-      store4(out + base + 4 * (threadIdx.x + 128 * j), normalised(xv[j], mean, rstd, wv[j], bv[j]));
+    if (threadIdx.x + THREADS * j < pieces)
+      store4(out + base + 4 * (threadIdx.x + THREADS * j), normalised(xv[j], mean, rstd, wv[j], bv[j]));
 }
 
 template <typename T>
@@ -328,20 +333,27 @@ MLR_EXPORT int mlr_layer_norm_step(float* x, const float* delta, const float* dw
   const size_t shared = sizeof(float) * ((size_t)width + 32);
   if (shared > 200 * 1024) return MLR_TOO_LARGE;
   auto aligned = [](const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; };
-  if (width % 4 == 0 && width <= 2048 && aligned(x) && aligned(delta) && aligned(dw) && aligned(db) && aligned(offset) &&
-      aligned(w) && aligned(b) && aligned(out)) {
-    if (rows <= 64) {
-      // few rows: a CTA per row, all operands asked for at once
-      if (out_dtype == MLR_F32)
-        launch_kernel(layer_norm_step_row_kernel<float>, dim3(rows), dim3(128), 0, stream, x, delta, dw, db, offset, w, b,
-                      (float*)out, width, eps);
-      else if (out_dtype == MLR_BF16)
-        launch_kernel(layer_norm_step_row_kernel<bf16>, dim3(rows), dim3(128), 0, stream, x, delta, dw, db, offset, w, b,
-                      (bf16*)out, width, eps);
-      else
-        return MLR_BAD_DTYPE;
+  const bool pieces_fit = width % 4 == 0 && aligned(x) && aligned(delta) && aligned(dw) && aligned(db) && aligned(offset) &&
+                          aligned(w) && aligned(b) && aligned(out);
+  if (pieces_fit && rows <= 64 && width <= 8192) {
+    // few rows: a CTA per row, all operands asked for at once
+    auto launch_row = [&](auto kernel, int threads, auto* typed_out) -> int {
+      launch_kernel(kernel, dim3(rows), dim3(threads), 0, stream, x, delta, dw, db, offset, w, b, typed_out, width, eps);
       return launch_status();
+    };
+    if (out_dtype == MLR_F32) {
+      if (width <= 2048) return launch_row(layer_norm_step_row_kernel<float, 128>, 128, (float*)out);
+      if (width <= 4096) return launch_row(layer_norm_step_row_kernel<float, 256>, 256, (float*)out);
+      return launch_row(layer_norm_step_row_kernel<float, 512>, 512, (float*)out);
     }
+    if (out_dtype == MLR_BF16) {
+      if (width <= 2048) return launch_row(layer_norm_step_row_kernel<bf16, 128>, 128, (bf16*)out);
+      if (width <= 4096) return launch_row(layer_norm_step_row_kernel<bf16, 256>, 256, (bf16*)out);
+      return launch_row(layer_norm_step_row_kernel<bf16, 512>, 512, (bf16*)out);
+    }
+    return MLR_BAD_DTYPE;
+  }
+  if (pieces_fit && width <= 2048) {
     // the row fits a warp's registers
     auto launch_warp = [&](auto kernel, auto* typed_out) -> int {
       launch_kernel(kernel, dim3((rows + 3) / 4), dim3(128), 0, stream, x, delta, dw, db, offset, w, b, typed_out, rows,
