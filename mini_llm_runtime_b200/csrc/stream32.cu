@@ -15,6 +15,8 @@
 // mlr_scale_inplace        x *= s for float32 x (logit scale).
 #include "common.cuh"
 
+#include <type_traits>
+
 namespace mlr {
 
 template <typename T>
@@ -200,7 +202,9 @@ __device__ __forceinline__ float block_sum_of(float v, float* scratch) {
   return total;
 }
 
-template <typename T, int THREADS>
+// EARLY: the norms' vectors are asked for before the wait and kept in registers (steps of few rows: one
+// trip to memory); otherwise they are read where they are used (many rows: more blocks per SM).
+template <typename T, int THREADS, bool EARLY>
 __global__ void __launch_bounds__(THREADS)
 layer_norm_step_row_kernel(float* x, const float* delta, const float* __restrict__ dw, const float* __restrict__ db,
                            const float* __restrict__ offset, const float* __restrict__ w, const float* __restrict__ b,
@@ -216,12 +220,20 @@ layer_norm_step_row_kernel(float* x, const float* delta, const float* __restrict
   for (int j = 0; j < CH; ++j) {
     const int c = threadIdx.x + THREADS * j;
     const bool in = c < pieces;
-    dwv[j] = in && delta != nullptr ? reinterpret_cast<const float4*>(dw)[c] : zero;
-    dbv[j] = in && delta != nullptr ? reinterpret_cast<const float4*>(db)[c] : zero;
-    ov[j] = in && offset != nullptr ? reinterpret_cast<const float4*>(offset)[c] : zero;
-    wv[j] = in && out != nullptr ? reinterpret_cast<const float4*>(w)[c] : zero;
-    bv[j] = in && out != nullptr ? reinterpret_cast<const float4*>(b)[c] : zero;
+    if (EARLY) {
+      dwv[j] = in && delta != nullptr ? reinterpret_cast<const float4*>(dw)[c] : zero;
+      dbv[j] = in && delta != nullptr ? reinterpret_cast<const float4*>(db)[c] : zero;
+      ov[j] = in && offset != nullptr ? reinterpret_cast<const float4*>(offset)[c] : zero;
+      wv[j] = in && out != nullptr ? reinterpret_cast<const float4*>(w)[c] : zero;
+      bv[j] = in && out != nullptr ? reinterpret_cast<const float4*>(b)[c] : zero;
+    }
   }
+  // piece j of a vector: from the registers, or from memory now
+  auto piece = [&](const float4 (&kept)[CH], const float* vector, int j) -> float4 {
+    if (EARLY) return kept[j];
+    const int c = threadIdx.x + THREADS * j;
+    return c < pieces ? reinterpret_cast<const float4*>(vector)[c] : zero;
+  };
   pdl_wait();
 #pragma unroll
   for (int j = 0; j < CH; ++j) {
@@ -245,13 +257,16 @@ layer_norm_step_row_kernel(float* x, const float* delta, const float* __restrict
     const float rstd = 1.f / sqrtf(block_sum_of<THREADS>(sq, scratch) / (float)width + eps);
 #pragma unroll
     for (int j = 0; j < CH; ++j) {
-      const float4 add = normalised(dv[j], mean, rstd, dwv[j], dbv[j]);
+      const float4 add = normalised(dv[j], mean, rstd, piece(dwv, dw, j), piece(dbv, db, j));
       xv[j].x += add.x; xv[j].y += add.y; xv[j].z += add.z; xv[j].w += add.w;
     }
   }
   if (offset != nullptr) {
 #pragma unroll
-    for (int j = 0; j < CH; ++j) { xv[j].x += ov[j].x; xv[j].y += ov[j].y; xv[j].z += ov[j].z; xv[j].w += ov[j].w; }
+    for (int j = 0; j < CH; ++j) {
+      const float4 o = piece(ov, offset, j);
+      xv[j].x += o.x; xv[j].y += o.y; xv[j].z += o.z; xv[j].w += o.w;
+    }
   }
   if (delta != nullptr || offset != nullptr) {
 #pragma unroll
@@ -275,7 +290,7 @@ layer_norm_step_row_kernel(float* x, const float* delta, const float* __restrict
 #pragma unroll
   for (int j = 0; j < CH; ++j)
     if (threadIdx.x + THREADS * j < pieces)
-      store4(out + base + 4 * (threadIdx.x + THREADS * j), normalised(xv[j], mean, rstd, wv[j], bv[j]));
+      store4(out + base + 4 * (threadIdx.x + THREADS * j), normalised(xv[j], mean, rstd, piece(wv, w, j), piece(bv, b, j)));
 }
 
 template <typename T>
@@ -335,22 +350,24 @@ MLR_EXPORT int mlr_layer_norm_step(float* x, const float* delta, const float* dw
   auto aligned = [](const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; };
   const bool pieces_fit = width % 4 == 0 && aligned(x) && aligned(delta) && aligned(dw) && aligned(db) && aligned(offset) &&
                           aligned(w) && aligned(b) && aligned(out);
-  if (pieces_fit && rows <= 64 && width <= 8192) {
-    // few rows: a CTA per row, all operands asked for at once
+  if (pieces_fit && width <= 8192 && (rows <= 64 || width > 2048)) {
+    // few rows, or rows too wide for a warp's registers: a CTA per row, all operands asked for at once
     auto launch_row = [&](auto kernel, int threads, auto* typed_out) -> int {
       launch_kernel(kernel, dim3(rows), dim3(threads), 0, stream, x, delta, dw, db, offset, w, b, typed_out, width, eps);
       return launch_status();
     };
-    if (out_dtype == MLR_F32) {
-      if (width <= 2048) return launch_row(layer_norm_step_row_kernel<float, 128>, 128, (float*)out);
-      if (width <= 4096) return launch_row(layer_norm_step_row_kernel<float, 256>, 256, (float*)out);
-      return launch_row(layer_norm_step_row_kernel<float, 512>, 512, (float*)out);
-    }
-    if (out_dtype == MLR_BF16) {
-      if (width <= 2048) return launch_row(layer_norm_step_row_kernel<bf16, 128>, 128, (bf16*)out);
-      if (width <= 4096) return launch_row(layer_norm_step_row_kernel<bf16, 256>, 256, (bf16*)out);
-      return launch_row(layer_norm_step_row_kernel<bf16, 512>, 512, (bf16*)out);
-    }
+    auto launch_typed = [&](auto* typed_out) -> int {
+      using T = std::remove_pointer_t<decltype(typed_out)>;
+      if (rows <= 64) {
+        if (width <= 2048) return launch_row(layer_norm_step_row_kernel<T, 128, true>, 128, typed_out);
+        if (width <= 4096) return launch_row(layer_norm_step_row_kernel<T, 256, true>, 256, typed_out);
+        return launch_row(layer_norm_step_row_kernel<T, 512, true>, 512, typed_out);
+      }
+      if (width <= 4096) return launch_row(layer_norm_step_row_kernel<T, 256, false>, 256, typed_out);
+      return launch_row(layer_norm_step_row_kernel<T, 512, false>, 512, typed_out);
+    };
+    if (out_dtype == MLR_F32) return launch_typed((float*)out);
+    if (out_dtype == MLR_BF16) return launch_typed((bf16*)out);
     return MLR_BAD_DTYPE;
   }
   if (pieces_fit && width <= 2048) {

@@ -137,7 +137,8 @@ def test_grouped_and_plain_products_share_a_kernel_without_harm():
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("heads,kv_heads,dim,vdim,rot,interleaved", [(6, 2, 16, 24, 16, True), (3, 3, 10, 6, 6, True),
                                                                       (4, 1, 64, 64, 32, False), (2, 2, 128, 64, 128, True),
-                                                                      (16, 4, 128, 128, 128, True), (32, 8, 128, 128, 64, True)])
+                                                                      (16, 4, 128, 128, 128, True), (32, 8, 128, 128, 64, True),
+                                                                      (2, 1, 32, 16, 16, False), (2, 2, 16, 8, 4, True)])
 def test_prepare_and_turn_kernels_against_their_formulas(heads, kv_heads, dim, vdim, rot, interleaved, dtype):
     from mini_llm_runtime_b200 import ops
     k = ops.current()

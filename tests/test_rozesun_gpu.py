@@ -52,7 +52,7 @@ def test_kernels_against_their_formulas():
     from mini_llm_runtime_b200 import ops
     k = ops.current()
     generator = torch.Generator().manual_seed(5)
-    for rows, width in [(1, 40), (7, 68), (33, 1000), (3, 5000), (5, 4096), (70, 4096), (2, 2052), (9, 8192), (4, 8196)]:
+    for rows, width in [(1, 40), (7, 68), (33, 1000), (3, 5000), (70, 5000), (5, 4096), (70, 4096), (2, 2052), (9, 8192), (4, 8196)]:
         x = torch.randn(rows, width, generator=generator) * 3 + 1
         delta = torch.randn(rows, width, generator=generator) * 2
         vectors = [torch.randn(width, generator=generator) for _ in range(5)]
