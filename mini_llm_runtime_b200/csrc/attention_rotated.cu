@@ -113,7 +113,7 @@ __device__ __forceinline__ void block_sum_two(float* a, float* b, float* scratch
 // THREADS: the block's size.  PRE: with 16-byte pieces, how many pieces of the NEXT row a thread asks for
 // while the block works on this one (a block then takes every gridDim.x-th row); 0: one row per block.
 template <typename T, int THREADS, int PRE>
-__global__ void __launch_bounds__(THREADS)
+__global__ void __launch_bounds__(THREADS, 1024 / THREADS)
 rotated_prepare_kernel(const float* qkv, const int* positions, const float* __restrict__ q_weight,
                        const float* __restrict__ k_weight, const float* __restrict__ key_freq,
                        const float* __restrict__ value_freq, const long long* slots, T* __restrict__ q_out, T* k_pool,
@@ -138,6 +138,9 @@ rotated_prepare_kernel(const float* qkv, const int* positions, const float* __re
     // takes four consecutive entries at a time (no bank conflicts, 8- or 16-byte stores).
     const int pieces = width >> 2;
     const int key_pairs = rot / 2, value_pairs = value_freq != nullptr ? vdim / 2 : 0;
+    // head sizes that are powers of two divide by a shift
+    const int dim_shift = (dim & (dim - 1)) == 0 ? __ffs(dim) - 1 : -1;
+    const int vdim_shift = (vdim & (vdim - 1)) == 0 ? __ffs(vdim) - 1 : -1;
     float4 ahead[PRE > 0 ? PRE : 1];
     int position_ahead = 0;
     long long slot_ahead = -1;
@@ -202,23 +205,29 @@ rotated_prepare_kernel(const float* qkv, const int* positions, const float* __re
       const float k_scale = k_weight != nullptr ? 1.f / sqrtf(k_sq / (float)wk + eps) : 1.f;
 
       const int pieces_q = wq >> 2, pieces_k = store ? wk >> 2 : 0, pieces_v = store ? wv >> 2 : 0;
+      T* q_row = q_out + (size_t)r * wq;
+      // a row's place in its page: head g lies g * page_size * size further on
+      T* k_row = k_pool + ((size_t)page * kv_heads * page_size + offset) * dim;
+      T* v_row = v_pool + ((size_t)page * kv_heads * page_size + offset) * vdim;
       for (int idx = threadIdx.x; idx < pieces_q + pieces_k + pieces_v; idx += THREADS) {
         if (idx < pieces_q + pieces_k) {
           const bool is_q = idx < pieces_q;
           const int e = (is_q ? idx : idx - pieces_q) << 2;
-          const int head = e / dim, d0 = e - head * dim;
+          const int head = dim_shift >= 0 ? e >> dim_shift : e / dim;
+          const int d0 = e - head * dim;
           const float* weight = is_q ? q_weight : k_weight;
           if (weight != nullptr) weight += head * dim;
-          const float4 y = turned4(row + (is_q ? 0 : wq) + head * dim, weight, is_q ? q_scale : k_scale, d0, rot,
-                                   interleaved, key_sine, key_cosine);
-          if (is_q) store4_as(q_out + (size_t)r * wq + e, y);
-          else store4_as(k_pool + (((size_t)page * kv_heads + head) * page_size + offset) * dim + d0, y);
+          const float4 y = turned4(row + (is_q ? e : wq + e) - d0, weight, is_q ? q_scale : k_scale, d0, rot, interleaved,
+                                   key_sine, key_cosine);
+          if (is_q) store4_as(q_row + e, y);
+          else store4_as(k_row + head * (page_size * dim) + d0, y);
         } else {
           const int e = (idx - pieces_q - pieces_k) << 2;
-          const int g = e / vdim, d0 = e - g * vdim;
-          const float4 y = turned4(row + wq + wk + g * vdim, nullptr, value_scale[g], d0, value_freq != nullptr ? vdim : 0,
+          const int g = vdim_shift >= 0 ? e >> vdim_shift : e / vdim;
+          const int d0 = e - g * vdim;
+          const float4 y = turned4(row + wq + wk + e - d0, nullptr, value_scale[g], d0, value_freq != nullptr ? vdim : 0,
                                    interleaved, value_sine, value_cosine);
-          store4_as(v_pool + (((size_t)page * kv_heads + g) * page_size + offset) * vdim + d0, y);
+          store4_as(v_row + g * (page_size * vdim) + d0, y);
         }
       }
       __syncthreads();                                  // the next row overwrites what this one read
