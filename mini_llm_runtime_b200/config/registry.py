@@ -15,6 +15,7 @@ from typing import Any, Callable, Mapping
 
 from .bopilorn import BopilornConfig, bopilorn_model_spec
 from .qwen2 import Qwen2Config, qwen2_model_spec
+from .ratilorn import RatilornConfig, ratilorn_model_spec
 from .rozesun import RozesunConfig, rozesun_model_spec
 from .spec import ModelSpec
 from .zazasun import ZazasunConfig, zazasun_model_spec
@@ -85,3 +86,4 @@ register_architecture(Qwen2Config.architecture, Qwen2Config.from_dict, qwen2_mod
 register_architecture(ZazasunConfig.architecture, ZazasunConfig.from_dict, zazasun_model_spec)
 register_architecture(RozesunConfig.architecture, RozesunConfig.from_dict, rozesun_model_spec)
 register_architecture(BopilornConfig.architecture, BopilornConfig.from_dict, bopilorn_model_spec)
+register_architecture(RatilornConfig.architecture, RatilornConfig.from_dict, ratilorn_model_spec)

@@ -3,10 +3,10 @@
 // mlr_route_experts      logits z = R x in float32 (R float32 [experts, K]; a CTA per eight rows and eight
 //                        experts), then a warp per row: scores s = softmax(z) (or sigmoid(z)), choice scores
 //                        c = s + correction; experts
-//                        form `groups` equal groups of neighbours, a group's score is its largest choice
-//                        score, only experts of the `keep` best groups can be chosen; the `top` largest
+//                        form `groups` equal groups of neighbours, a group's score is the sum of its `group_top`
+//                        largest choice scores (1: its largest), only experts of the `keep` best groups can be chosen; the `top` largest
 //                        choice scores win (ties: the lower index); the weights are the winners' s,
-//                        divided by their sum if asked.  chosen int32 [rows, top], weights float32.
+//                        divided by their sum + renorm_eps if asked.  chosen int32 [rows, top], weights float32.
 // mlr_expert_hidden      for every (row, chosen expert) pair p: hidden[p] = act(Wg_e x) * (Wu_e x), a warp
 //                        per four outputs, the dot products split over the lanes in a fixed order.
 // mlr_expert_down        out[row] = sum_t weights[row, t] * (Wd_e(t) hidden[row * top + t]) in float32, t
@@ -141,7 +141,8 @@ router_logits_kernel(const T* x, const float* __restrict__ router, float* logits
 // The choice, one warp per row, from the row's logits.
 __global__ void __launch_bounds__(CHOOSE_WARPS * 32)
 choose_experts_kernel(const float* logits, const float* __restrict__ correction, int* chosen, float* weights, int rows,
-                      int experts, int top, int groups, int keep, int sigmoid_scores, int renormalise) {
+                      int experts, int top, int groups, int keep, int group_top, int sigmoid_scores, int renormalise,
+                      float renorm_eps) {
   pdl_trigger();
   extern __shared__ __align__(16) float shared[];      // per warp: [experts] scores, [experts] choice scores, [groups]
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -176,9 +177,25 @@ choose_experts_kernel(const float* logits, const float* __restrict__ correction,
   const int size = experts / groups;
   if (keep < groups) {
     for (int g = lane; g < groups; g += 32) {
-      float best = -INFINITY;
-      for (int j = 0; j < size; ++j) best = fmaxf(best, choice[g * size + j]);
-      group_score[g] = best;
+      // the sum of the group's `group_top` largest choice scores (1: its largest), taken largest first
+      float total = 0.f, bound = INFINITY;
+      int bound_at = -1;
+      for (int n = 0; n < group_top && n < size; ++n) {
+        float best = -INFINITY;
+        int best_at = size;
+        for (int j = 0; j < size; ++j) {
+          const float c = choice[g * size + j];
+          const bool below = c < bound || (c == bound && j > bound_at);      // not one of those already taken
+          if (below && c > best) {
+            best = c;
+            best_at = j;
+          }
+        }
+        total = n == 0 ? best : total + best;
+        bound = best;
+        bound_at = best_at;
+      }
+      group_score[g] = total;
     }
     __syncwarp();
     // rank of every group: groups with a larger score, or an equal one and a lower index, come first
@@ -225,7 +242,7 @@ choose_experts_kernel(const float* logits, const float* __restrict__ correction,
     __syncwarp();
   }
   if (renormalise && lane == 0)
-    for (int t = 0; t < top; ++t) weights[(size_t)row * top + t] /= weight_sum;
+    for (int t = 0; t < top; ++t) weights[(size_t)row * top + t] /= (weight_sum + renorm_eps);
 }
 
 
@@ -447,10 +464,11 @@ MLR_DEFINE_PDL_SWITCH
 // x: [rows, K] in `dtype`; router: float32 [experts, K]; correction: float32 [experts] or null;
 // logits: float32 [rows, experts] (scratch); chosen: int32 [rows, top]; weights: float32 [rows, top].
 MLR_EXPORT int mlr_route_experts(const void* x, const float* router, const float* correction, float* logits, int* chosen,
-                                 float* weights, int rows, int K, int experts, int top, int groups, int keep,
-                                 int sigmoid_scores, int renormalise, int dtype, cudaStream_t stream) {
+                                 float* weights, int rows, int K, int experts, int top, int groups, int keep, int group_top,
+                                 int sigmoid_scores, int renormalise, float renorm_eps, int dtype, cudaStream_t stream) {
   if (rows == 0) return MLR_OK;
   if (rows < 0 || K <= 0 || experts <= 0 || top <= 0 || groups <= 0 || keep <= 0 || keep > groups || experts % groups != 0 ||
+      group_top <= 0 ||
       top > keep * (experts / groups))
     return MLR_BAD_SIZE;
   // as many rows per CTA as there are and fit (each router entry is then loaded once for all of them)
@@ -486,8 +504,8 @@ MLR_EXPORT int mlr_route_experts(const void* x, const float* router, const float
     if (err != cudaSuccess) return (int)err;
   }
   launch_kernel(choose_experts_kernel, dim3((rows + CHOOSE_WARPS - 1) / CHOOSE_WARPS), dim3(CHOOSE_WARPS * 32), choose_shared,
-                stream, (const float*)logits, correction, chosen, weights, rows, experts, top, groups, keep, sigmoid_scores,
-                renormalise);
+                stream, (const float*)logits, correction, chosen, weights, rows, experts, top, groups, keep, group_top,
+                sigmoid_scores, renormalise, renorm_eps);
   return launch_status();
 }
 

@@ -1,0 +1,286 @@
+// Kernels of a selective state-space mixer with a scalar decay per head (the "state-space duality"
+// form): a short causal convolution per channel whose last inputs are carried per request, the
+// recurrence itself, and the gated, grouped RMS norm behind it.  Everything here is float32; the
+// projections around it are products of their own.
+//
+// mlr_causal_conv        out[t, c] = act(bias[c] + sum_k w[c, k] u[t - (taps - 1) + k, c]) over the tokens
+//                        of each request, the inputs before the step's first token coming from the
+//                        request's state [taps - 1, channels] (zeros for a new request), which then
+//                        receives the step's last inputs.  act: silu (1) or none (0).
+// mlr_state_space_scan   per request, head h and token t, with g(h) = h / (heads / groups):
+//                          dt = softplus(dt_raw[t, h] + dt_bias[h]);  a = exp(-exp(A_log[h]) dt)
+//                          S <- a S + dt B[t, g] x[t, h]^T            (S: [state, vdim], kept as [vdim, state])
+//                          y[t, h] = S^T C[t, g] + D[h] x[t, h]
+//                        token by token in a fixed order, so a request's numbers do not depend on how its
+//                        tokens were cut into steps.
+// mlr_gated_group_norm   out = RMSnorm_parts(y * silu(z)) * weight: the row is cut into `parts` equal parts,
+//                        each divided by its own root mean square (eps inside the root).
+#include "common.cuh"
+
+#include <type_traits>
+
+namespace mlr {
+
+constexpr int MAX_TAPS = 16;
+
+// The request's new carried inputs: the last taps - 1 inputs of (old carried inputs, the step's rows).
+__device__ __forceinline__ void carry_inputs(const float* u, long long u_stride, float* state, int channels, int c,
+                                             int q_start, int q_len, int taps) {
+  float kept[MAX_TAPS - 1];
+#pragma unroll
+  for (int i = 0; i < MAX_TAPS - 1; ++i) {
+    if (i < taps - 1) {
+      const int t = q_len - (taps - 1) + i;       // relative to the step's first row
+      kept[i] = t >= 0 ? __ldcg(u + (size_t)(q_start + t) * u_stride + c) : state[(size_t)(taps - 1 + t) * channels + c];
+    }
+  }
+#pragma unroll
+  for (int i = 0; i < MAX_TAPS - 1; ++i)
+    if (i < taps - 1) state[(size_t)i * channels + c] = kept[i];
+}
+
+constexpr int CONV_TOKENS = 16;     // tokens one thread walks
+
+// grid: (channel blocks, segments, token chunks).  A one-row segment's thread also advances the state;
+// longer segments leave that to carry_kernel (their readers and the writer would race otherwise).
+__global__ void __launch_bounds__(128)
+causal_conv_kernel(const float* u, long long u_stride, const float* __restrict__ weight, const float* __restrict__ bias,
+                   float* states, float* out, const int* __restrict__ seg_q_start, const int* __restrict__ seg_q_len,
+                   const int* __restrict__ seg_slot, int channels, int taps, int act) {
+  pdl_trigger();
+  const int c = blockIdx.x * blockDim.x + threadIdx.x;
+  const int seg = blockIdx.y;
+  float w[MAX_TAPS];
+#pragma unroll
+  for (int k = 0; k < MAX_TAPS; ++k) w[k] = (k < taps && c < channels) ? weight[(size_t)c * taps + k] : 0.f;
+  const float b = (bias != nullptr && c < channels) ? bias[c] : 0.f;
+  pdl_wait();
+  if (c >= channels) return;
+  const int q_start = seg_q_start[seg], q_len = seg_q_len[seg];
+  const int t0 = blockIdx.z * CONV_TOKENS;
+  if (t0 >= q_len) return;
+  float* state = states + (size_t)seg_slot[seg] * (taps - 1) * channels;
+  const int t_end = min(q_len, t0 + CONV_TOKENS);
+  for (int t = t0; t < t_end; ++t) {
+    float sum = b;
+#pragma unroll
+    for (int k = 0; k < MAX_TAPS; ++k) {
+      if (k < taps) {
+        const int s = t - (taps - 1) + k;
+        const float v = s >= 0 ? __ldcg(u + (size_t)(q_start + s) * u_stride + c) : state[(size_t)(taps - 1 + s) * channels + c];
+        sum = fmaf(w[k], v, sum);
+      }
+    }
+    if (act == 1) sum = sum / (1.f + expf(-sum));
+    out[(size_t)(q_start + t) * channels + c] = sum;
+  }
+  if (q_len == 1) carry_inputs(u, u_stride, state, channels, c, q_start, q_len, taps);
+}
+
+__global__ void __launch_bounds__(128)
+carry_kernel(const float* u, long long u_stride, float* states, const int* __restrict__ seg_q_start,
+             const int* __restrict__ seg_q_len, const int* __restrict__ seg_slot, int channels, int taps) {
+  pdl_trigger();
+  pdl_wait();
+  const int c = blockIdx.x * blockDim.x + threadIdx.x;
+  const int seg = blockIdx.y;
+  if (c >= channels) return;
+  const int q_len = seg_q_len[seg];
+  if (q_len <= 1) return;
+  carry_inputs(u, u_stride, states + (size_t)seg_slot[seg] * (taps - 1) * channels, channels, c, seg_q_start[seg], q_len, taps);
+}
+
+constexpr int SCAN_NPT = 16;        // state entries of one value channel a thread holds
+constexpr int SCAN_TOKENS = 32;     // tokens staged at once
+constexpr int SCAN_THREADS = 128;
+
+struct ScanArgs {
+  const float *x, *B, *C, *dt_raw;
+  long long x_stride, b_stride, c_stride, dt_stride;
+  const float *dt_bias, *A_log, *D;
+  float* states;
+  float* y;
+  const int *seg_q_start, *seg_q_len, *seg_slot;
+  int heads, vdim, n, groups;
+};
+
+// SL: threads that share one value channel's state (a power of two; SL * SCAN_NPT >= n).  Lane l of a warp
+// holds entries [s * 16, s * 16 + 16) of channel p with s = l % SL, p = l / SL.
+// grid: (segments, heads, value-channel blocks).
+template <int SL>
+__global__ void __launch_bounds__(SCAN_THREADS)
+state_space_scan_kernel(ScanArgs a) {
+  pdl_trigger();
+  extern __shared__ __align__(16) float shared[];
+  constexpr int P_CTA = SCAN_THREADS / SL;
+  const int N = a.n, P = a.vdim;
+  float* b_rows = shared;                             // [SCAN_TOKENS][N], already times dt
+  float* c_rows = b_rows + SCAN_TOKENS * N;           // [SCAN_TOKENS][N]
+  float* x_rows = c_rows + SCAN_TOKENS * N;           // [SCAN_TOKENS][P_CTA]
+  float* decay = x_rows + SCAN_TOKENS * P_CTA;        // [SCAN_TOKENS]
+  float* step = decay + SCAN_TOKENS;                  // [SCAN_TOKENS]
+  const int seg = blockIdx.x, head = blockIdx.y;
+  const int group = head / (a.heads / a.groups);
+  const int s = threadIdx.x % SL, p_local = threadIdx.x / SL;
+  const int p = blockIdx.z * P_CTA + p_local;
+  const float rate = expf(a.A_log[head]), bias = a.dt_bias[head], skip = a.D[head];
+  pdl_wait();
+  const int q_start = a.seg_q_start[seg], q_len = a.seg_q_len[seg];
+  float* state = a.states + (((size_t)a.seg_slot[seg] * a.heads + head) * P + (p < P ? p : 0)) * N;
+  float S[SCAN_NPT];
+#pragma unroll
+  for (int i = 0; i < SCAN_NPT; ++i) {
+    const int n = s * SCAN_NPT + i;
+    S[i] = (p < P && n < N) ? state[n] : 0.f;
+  }
+  for (int t0 = 0; t0 < q_len; t0 += SCAN_TOKENS) {
+    const int tokens = min(SCAN_TOKENS, q_len - t0);
+    __syncthreads();
+    if (threadIdx.x < tokens) {
+      const float raw = __ldcg(a.dt_raw + (size_t)(q_start + t0 + threadIdx.x) * a.dt_stride + head) + bias;
+      const float dt = raw > 20.f ? raw : log1pf(expf(raw));
+      step[threadIdx.x] = dt;
+      decay[threadIdx.x] = expf(-rate * dt);
+    }
+    __syncthreads();
+    for (int idx = threadIdx.x; idx < tokens * N; idx += SCAN_THREADS) {
+      const int t = idx / N, n = idx - t * N;
+      const size_t row = (size_t)(q_start + t0 + t);
+      b_rows[idx] = __ldcg(a.B + row * a.b_stride + (size_t)group * N + n) * step[t];
+      c_rows[idx] = __ldcg(a.C + row * a.c_stride + (size_t)group * N + n);
+    }
+    for (int idx = threadIdx.x; idx < tokens * P_CTA; idx += SCAN_THREADS) {
+      const int t = idx / P_CTA, pl = idx - t * P_CTA;
+      const int pp = blockIdx.z * P_CTA + pl;
+      x_rows[idx] = pp < P ? __ldcg(a.x + (size_t)(q_start + t0 + t) * a.x_stride + (size_t)head * P + pp) : 0.f;
+    }
+    __syncthreads();
+    for (int t = 0; t < tokens; ++t) {
+      const float av = decay[t], xv = x_rows[t * P_CTA + p_local];
+      const float* bt = b_rows + t * N + s * SCAN_NPT;
+      const float* ct = c_rows + t * N + s * SCAN_NPT;
+      float sum = 0.f;
+#pragma unroll
+      for (int i = 0; i < SCAN_NPT; ++i) {
+        if (s * SCAN_NPT + i < N) {
+          S[i] = fmaf(av, S[i], bt[i] * xv);
+          sum = fmaf(S[i], ct[i], sum);
+        }
+      }
+#pragma unroll
+      for (int offset = SL / 2; offset > 0; offset >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, offset);
+      if (s == 0 && p < P) a.y[(size_t)(q_start + t0 + t) * a.heads * P + (size_t)head * P + p] = fmaf(skip, xv, sum);
+    }
+  }
+  if (p < P) {
+#pragma unroll
+    for (int i = 0; i < SCAN_NPT; ++i) {
+      const int n = s * SCAN_NPT + i;
+      if (n < N) state[n] = S[i];
+    }
+  }
+}
+
+// grid: (rows, parts)
+template <typename T>
+__global__ void __launch_bounds__(256)
+gated_group_norm_kernel(const float* y, const float* z, long long z_stride, const float* __restrict__ weight,
+                        T* __restrict__ out, int inner, int parts, float eps) {
+  pdl_trigger();
+  extern __shared__ float staged[];      // [inner / parts] + 32
+  const int width = inner / parts;
+  float* scratch = staged + width;
+  const int row = blockIdx.x, first = blockIdx.y * width;
+  pdl_wait();
+  float sq = 0.f;
+  for (int d = threadIdx.x; d < width; d += blockDim.x) {
+    const float gate = z == nullptr ? 1.f : __ldcg(z + (size_t)row * z_stride + first + d);
+    const float v = __ldcg(y + (size_t)row * inner + first + d) * (z == nullptr ? 1.f : gate / (1.f + expf(-gate)));
+    staged[d] = v;
+    sq = fmaf(v, v, sq);
+  }
+  const float rstd = 1.f / sqrtf(block_sum(sq, scratch) / (float)width + eps);
+  for (int d = threadIdx.x; d < width; d += blockDim.x)
+    out[(size_t)row * inner + first + d] = from_float<T>(staged[d] * rstd * weight[first + d]);
+}
+
+}  // namespace mlr
+
+using namespace mlr;
+
+MLR_DEFINE_PDL_SWITCH
+
+// u: float32 rows of `channels` entries spaced u_stride apart; weight: float32 [channels, taps]; bias:
+// float32 [channels] or null; states: float32 [slots, taps - 1, channels]; out: float32 [rows, channels].
+MLR_EXPORT int mlr_causal_conv(const float* u, long long u_stride, const float* weight, const float* bias, float* states,
+                               float* out, const int* seg_q_start, const int* seg_q_len, const int* seg_slot, int segments,
+                               int max_q_len, int channels, int taps, int act, cudaStream_t stream) {
+  if (segments == 0) return MLR_OK;
+  if (segments < 0 || max_q_len <= 0 || channels <= 0 || taps < 2) return MLR_BAD_SIZE;
+  if (taps > MAX_TAPS || segments > 65535) return MLR_TOO_LARGE;
+  const int chunks = (max_q_len + CONV_TOKENS - 1) / CONV_TOKENS;
+  if (chunks > 65535) return MLR_TOO_LARGE;
+  launch_kernel(causal_conv_kernel, dim3((channels + 127) / 128, segments, chunks), dim3(128), 0, stream, u, u_stride, weight,
+                bias, states, out, seg_q_start, seg_q_len, seg_slot, channels, taps, act);
+  int status = launch_status();
+  if (status != MLR_OK || max_q_len == 1) return status;
+  launch_kernel(carry_kernel, dim3((channels + 127) / 128, segments), dim3(128), 0, stream, u, u_stride, states, seg_q_start,
+                seg_q_len, seg_slot, channels, taps);
+  return launch_status();
+}
+
+// x: float32 rows of heads*vdim entries; B, C: rows of groups*n entries; dt_raw: rows of `heads` entries
+// (each with its own row stride); dt_bias, A_log, D: float32 [heads]; states: float32 [slots, heads, vdim, n];
+// y: float32 [rows, heads*vdim].
+MLR_EXPORT int mlr_state_space_scan(const float* x, long long x_stride, const float* B, long long b_stride, const float* C,
+                                    long long c_stride, const float* dt_raw, long long dt_stride, const float* dt_bias,
+                                    const float* A_log, const float* D, float* states, float* y, const int* seg_q_start,
+                                    const int* seg_q_len, const int* seg_slot, int segments, int heads, int vdim, int n,
+                                    int groups, cudaStream_t stream) {
+  if (segments == 0) return MLR_OK;
+  if (segments < 0 || heads <= 0 || vdim <= 0 || n <= 0 || groups <= 0 || heads % groups != 0) return MLR_BAD_SIZE;
+  if (n > 32 * SCAN_NPT || heads > 65535) return MLR_TOO_LARGE;
+  ScanArgs a{x, B, C, dt_raw, x_stride, b_stride, c_stride, dt_stride, dt_bias, A_log, D, states, y,
+             seg_q_start, seg_q_len, seg_slot, heads, vdim, n, groups};
+  int slices = 1;
+  while (slices * SCAN_NPT < n) slices *= 2;
+  auto launch = [&](auto kernel, int sl) -> int {
+    const int p_cta = SCAN_THREADS / sl;
+    const size_t shared = sizeof(float) * ((size_t)SCAN_TOKENS * (2 * n + p_cta) + 2 * SCAN_TOKENS);
+    if (shared > 48 * 1024) {
+      cudaError_t err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)shared);
+      if (err != cudaSuccess) return (int)err;
+    }
+    launch_kernel(kernel, dim3(segments, heads, (vdim + p_cta - 1) / p_cta), dim3(SCAN_THREADS), shared, stream, a);
+    return launch_status();
+  };
+  switch (slices) {
+    case 1: return launch(state_space_scan_kernel<1>, 1);
+    case 2: return launch(state_space_scan_kernel<2>, 2);
+    case 4: return launch(state_space_scan_kernel<4>, 4);
+    case 8: return launch(state_space_scan_kernel<8>, 8);
+    case 16: return launch(state_space_scan_kernel<16>, 16);
+    default: return launch(state_space_scan_kernel<32>, 32);
+  }
+}
+
+// y: float32 [rows, inner]; z: float32 rows of `inner` entries spaced z_stride apart, or null (no gate);
+// weight: float32 [inner]; out: [rows, inner] in out_dtype.
+MLR_EXPORT int mlr_gated_group_norm(const float* y, const float* z, long long z_stride, const float* weight, void* out,
+                                    int rows, int inner, int parts, float eps, int out_dtype, cudaStream_t stream) {
+  if (rows == 0) return MLR_OK;
+  if (rows < 0 || inner <= 0 || parts <= 0 || inner % parts != 0) return MLR_BAD_SIZE;
+  const size_t shared = sizeof(float) * ((size_t)inner / parts + 32);
+  if (shared > 200 * 1024 || parts > 65535) return MLR_TOO_LARGE;
+  auto launch = [&](auto kernel, auto* typed) -> int {
+    if (shared > 48 * 1024) {
+      cudaError_t err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)shared);
+      if (err != cudaSuccess) return (int)err;
+    }
+    launch_kernel(kernel, dim3(rows, parts), dim3(256), shared, stream, y, z, z_stride, weight, typed, inner, parts, eps);
+    return launch_status();
+  };
+  if (out_dtype == MLR_F32) return launch(gated_group_norm_kernel<float>, (float*)out);
+  if (out_dtype == MLR_BF16) return launch(gated_group_norm_kernel<bf16>, (bf16*)out);
+  return MLR_BAD_DTYPE;
+}

@@ -10,6 +10,11 @@
 //                            out = LN(x; w, b)           the input of the next sublayer, compute dtype
 //                          LN(v; w, b) = (v - mean) / sqrt(var + eps) * w + b with var the mean of the
 //                          squared deviations; all sums in float32 in an order fixed by the width.
+// mlr_rms_norm_step        the same pass for sublayers that are normalised on their way into the stream by
+//                          an RMS norm (no centering, no bias): x += delta / rms(delta) * dw, then
+//                          out = x / rms(x) * w, or the rows of x as they are in the compute dtype when
+//                          no w is given (the input of a sublayer that reads the stream itself).
+// mlr_normed_mean          out = factor * (a / rms(a) * wa + b / rms(b) * wb) for two float32 inputs.
 // mlr_clamped_gate         y = g * sigmoid(slope * g) * (u + 1) with g = min(gate, limit) and
 //                          u = clamp(up, -limit, limit), on rows of gate/up blocks.
 // mlr_scale_inplace        x *= s for float32 x (logit scale).
@@ -293,6 +298,64 @@ layer_norm_step_row_kernel(float* x, const float* delta, const float* __restrict
       store4(out + base + 4 * (threadIdx.x + THREADS * j), normalised(xv[j], mean, rstd, piece(wv, w, j), piece(bv, b, j)));
 }
 
+// 1 / sqrt(mean(v^2) + eps) of `width` floats in shared memory; every thread gets it.
+__device__ __forceinline__ float row_inverse_rms(const float* values, int width, float eps, float* scratch) {
+  float sq = 0.f;
+  for (int d = threadIdx.x; d < width; d += blockDim.x) sq = fmaf(values[d], values[d], sq);
+  return 1.f / sqrtf(block_sum(sq, scratch) / (float)width + eps);
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256)
+rms_norm_step_kernel(float* x, const float* delta, const float* __restrict__ dw, const float* __restrict__ w,
+                     T* __restrict__ out, int width, float eps) {
+  pdl_trigger();
+  extern __shared__ float staged[];      // [width] + 32
+  float* scratch = staged + width;
+  const size_t base = (size_t)blockIdx.x * width;
+  pdl_wait();
+  if (delta != nullptr) {
+    for (int d = threadIdx.x; d < width; d += blockDim.x) staged[d] = __ldcg(delta + base + d);
+    __syncthreads();
+    const float rstd = row_inverse_rms(staged, width, eps, scratch);
+    for (int d = threadIdx.x; d < width; d += blockDim.x) {
+      const float v = __ldcg(x + base + d) + staged[d] * rstd * dw[d];
+      staged[d] = v;
+      x[base + d] = v;
+    }
+  } else {
+    for (int d = threadIdx.x; d < width; d += blockDim.x) staged[d] = __ldcg(x + base + d);
+  }
+  if (out == nullptr) return;
+  if (w == nullptr) {
+    for (int d = threadIdx.x; d < width; d += blockDim.x) out[base + d] = from_float<T>(staged[d]);      // own entries
+    return;
+  }
+  __syncthreads();
+  const float rstd = row_inverse_rms(staged, width, eps, scratch);
+  for (int d = threadIdx.x; d < width; d += blockDim.x) out[base + d] = from_float<T>(staged[d] * rstd * w[d]);
+}
+
+__global__ void __launch_bounds__(256)
+normed_mean_kernel(const float* a, const float* __restrict__ wa, const float* b, const float* __restrict__ wb,
+                   float* __restrict__ out, int width, float eps, float factor) {
+  pdl_trigger();
+  extern __shared__ float staged[];      // [2 * width] + 32
+  float* second = staged + width;
+  float* scratch = second + width;
+  const size_t base = (size_t)blockIdx.x * width;
+  pdl_wait();
+  for (int d = threadIdx.x; d < width; d += blockDim.x) {
+    staged[d] = __ldcg(a + base + d);
+    second[d] = __ldcg(b + base + d);
+  }
+  __syncthreads();
+  const float ra = row_inverse_rms(staged, width, eps, scratch);
+  const float rb = row_inverse_rms(second, width, eps, scratch);
+  for (int d = threadIdx.x; d < width; d += blockDim.x)
+    out[base + d] = factor * (staged[d] * ra * wa[d] + second[d] * rb * wb[d]);
+}
+
 template <typename T>
 __global__ void __launch_bounds__(256)
 clamped_gate_kernel(const T* x, T* __restrict__ out, long long rows, int inner, int block, float limit, float slope) {
@@ -400,6 +463,43 @@ MLR_EXPORT int mlr_layer_norm_step(float* x, const float* delta, const float* dw
   if (out_dtype == MLR_F32) return launch(layer_norm_step_kernel<float>, (float*)out);
   if (out_dtype == MLR_BF16) return launch(layer_norm_step_kernel<bf16>, (bf16*)out);
   return MLR_BAD_DTYPE;
+}
+
+// x: float32 [rows, width], updated in place when delta is given.  delta: float32 [rows, width] or null
+// (then dw is not read); dw, w: float32 [width]; out: [rows, width] in out_dtype or null.  With out and no
+// w, out receives the rows of x (after the add) as they are.
+MLR_EXPORT int mlr_rms_norm_step(float* x, const float* delta, const float* dw, const float* w, void* out, int rows,
+                                 int width, float eps, int out_dtype, cudaStream_t stream) {
+  if (rows == 0) return MLR_OK;
+  if (rows < 0 || width <= 0 || (delta != nullptr && dw == nullptr)) return MLR_BAD_SIZE;
+  const size_t shared = sizeof(float) * ((size_t)width + 32);
+  if (shared > 200 * 1024) return MLR_TOO_LARGE;
+  auto launch = [&](auto kernel, auto* typed_out) -> int {
+    if (shared > 48 * 1024) {
+      cudaError_t err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)shared);
+      if (err != cudaSuccess) return (int)err;
+    }
+    launch_kernel(kernel, dim3(rows), dim3(256), shared, stream, x, delta, dw, w, typed_out, width, eps);
+    return launch_status();
+  };
+  if (out_dtype == MLR_F32) return launch(rms_norm_step_kernel<float>, (float*)out);
+  if (out_dtype == MLR_BF16) return launch(rms_norm_step_kernel<bf16>, (bf16*)out);
+  return MLR_BAD_DTYPE;
+}
+
+// a, b, out: float32 [rows, width]; wa, wb: float32 [width].
+MLR_EXPORT int mlr_normed_mean(const float* a, const float* wa, const float* b, const float* wb, float* out, int rows,
+                               int width, float eps, float factor, cudaStream_t stream) {
+  if (rows == 0) return MLR_OK;
+  if (rows < 0 || width <= 0) return MLR_BAD_SIZE;
+  const size_t shared = sizeof(float) * (2 * (size_t)width + 32);
+  if (shared > 200 * 1024) return MLR_TOO_LARGE;
+  if (shared > 48 * 1024) {
+    cudaError_t err = cudaFuncSetAttribute(normed_mean_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)shared);
+    if (err != cudaSuccess) return (int)err;
+  }
+  launch_kernel(normed_mean_kernel, dim3(rows), dim3(256), shared, stream, a, wa, b, wb, out, width, eps, factor);
+  return launch_status();
 }
 
 MLR_EXPORT int mlr_clamped_gate(const void* x, void* out, long long rows, int inner, int block, float limit, float slope,

@@ -105,6 +105,7 @@ class StepContext:
     max_kv_len: int = 0
     views: dict[int, CacheView] = field(default_factory=dict)
     plans: dict = field(default_factory=dict)       # plan key -> (device arrays by name, counts by name)
+    shared: dict = field(default_factory=dict)      # what a layer hands to later layers of the same step, by name
     wanted_all_rows: bool = False    # wanted_rows is 0, 1, .., rows-1 (a decode step): no gather needed
     wanted_slot: torch.Tensor | None = None     # int32 [wanted]: slot of each wanted row's request (sampling)
 

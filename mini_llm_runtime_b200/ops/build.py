@@ -50,6 +50,8 @@ LIBRARIES: dict[str, tuple[str, ...]] = {
     "attention_latent_mma": (),
     "attention_rotated": (),
     "routed_experts": (),
+    "attention_sigmoid": (),
+    "state_space": (),
 }
 
 _loaded: dict[str, ctypes.CDLL] = {}

@@ -1309,11 +1309,13 @@ class CudaOps:
     # ------------------------------------------------------------------ routed experts
     def route_experts(self, x: torch.Tensor, router: torch.Tensor, correction: torch.Tensor | None, top: int,
                       groups: int = 1, keep: int = 1, scoring: str = "softmax",
-                      renormalise: bool = False) -> tuple[torch.Tensor, torch.Tensor]:
+                      renormalise: bool = False, group_top: int = 1,
+                      renorm_eps: float = 0.0) -> tuple[torch.Tensor, torch.Tensor]:
         """Router of a mixture of experts, in float32: scores = softmax (or sigmoid) of router x; the ``top``
         largest of scores + correction among the experts of the ``keep`` best of ``groups`` groups are
         chosen (int32 [rows, top]); their weights are their scores (float32 [rows, top]), divided by
-        their sum with ``renormalise``."""
+        their sum + ``renorm_eps`` with ``renormalise``.  A group's rank comes from the sum of its
+        ``group_top`` largest choice scores (1: its largest)."""
         _need(x, "x", dims=2)
         _need(router, "router", torch.float32, 2)
         experts = router.shape[0]
@@ -1330,8 +1332,8 @@ class CudaOps:
         logits = torch.empty((x.shape[0], experts), dtype=torch.float32, device=x.device)
         _check(build.load_library("routed_experts").mlr_route_experts(
             _ptr(x), _ptr(router), _ptr(correction), _ptr(logits), _ptr(chosen), _ptr(weights), x.shape[0], x.shape[1], experts,
-            int(top), int(groups), int(keep), int(scoring == "sigmoid"), int(bool(renormalise)), _code(x.dtype),
-            _stream()), "route_experts")
+            int(top), int(groups), int(keep), int(group_top), int(scoring == "sigmoid"), int(bool(renormalise)),
+            ctypes.c_float(renorm_eps), _code(x.dtype), _stream()), "route_experts")
         return chosen, weights
 
     def routed_experts(self, x: torch.Tensor, chosen: torch.Tensor, weights: torch.Tensor, gate_up: torch.Tensor,
@@ -1404,6 +1406,196 @@ class CudaOps:
                                              N, inner, 1, 0, tile_rows, error_word, _stream()), "grouped down product")
         _check(lib.mlr_combine_pairs(_ptr(y), _ptr(place), _ptr(weights), _ptr(out), rows, N, top, _stream()),
                "combine_pairs")
+        return out
+
+    # ------------------------------------------------------------------ 32-bit stream with RMS norms behind the sublayers
+    def rms_norm_step(self, x: torch.Tensor, eps: float, *, delta: torch.Tensor | None = None,
+                      delta_weight: torch.Tensor | None = None, norm_weight: torch.Tensor | None = None,
+                      out_dtype: torch.dtype | None = None):
+        """One pass over the rows of the float32 stream ``x`` [rows, width]: x += delta / rms(delta) *
+        delta_weight (when ``delta``, float32, is given), then, with ``out_dtype``, returns x / rms(x) *
+        norm_weight in that dtype, or the rows of x as they are in that dtype when ``norm_weight`` is None.
+        rms(v) = sqrt(mean(v^2) + eps)."""
+        _need(x, "x", torch.float32, 2)
+        rows, width = x.shape
+        for name, vector in (("delta_weight", delta_weight), ("norm_weight", norm_weight)):
+            if vector is not None:
+                _need(vector, name, torch.float32, 1)
+                if vector.shape[0] != width:
+                    raise KernelError(f"{name} holds {vector.shape[0]} entries, rows have {width}")
+        if delta is not None:
+            _need(delta, "delta", torch.float32, 2)
+            if delta.shape != x.shape or delta_weight is None:
+                raise KernelError("delta needs the stream's shape and its norm's weight")
+        out = None if out_dtype is None else torch.empty((rows, width), dtype=out_dtype, device=x.device)
+        if delta is None and out is None:
+            return None
+        _check(build.load_library("stream32").mlr_rms_norm_step(
+            _ptr(x), _ptr(delta), _ptr(delta_weight), _ptr(norm_weight), _ptr(out), rows, width, ctypes.c_float(eps),
+            _code(out_dtype or torch.float32), _stream()), "rms_norm_step")
+        return out
+
+    def normed_mean(self, a: torch.Tensor, a_weight: torch.Tensor, b: torch.Tensor, b_weight: torch.Tensor, eps: float,
+                    factor: float) -> torch.Tensor:
+        """factor * (a / rms(a) * a_weight + b / rms(b) * b_weight), all float32, row by row."""
+        _need(a, "a", torch.float32, 2)
+        _need(b, "b", torch.float32, 2)
+        _need(a_weight, "a_weight", torch.float32, 1)
+        _need(b_weight, "b_weight", torch.float32, 1)
+        if a.shape != b.shape or a_weight.shape[0] != a.shape[1] or b_weight.shape[0] != a.shape[1]:
+            raise KernelError("normed_mean: shapes do not fit")
+        out = torch.empty_like(a)
+        _check(build.load_library("stream32").mlr_normed_mean(
+            _ptr(a), _ptr(a_weight), _ptr(b), _ptr(b_weight), _ptr(out), a.shape[0], a.shape[1], ctypes.c_float(eps),
+            ctypes.c_float(factor), _stream()), "normed_mean")
+        return out
+
+    # ------------------------------------------------------------------ plain-headed attention: prepare; sigmoid weights
+    def head_norm_kv_write(self, qkv: torch.Tensor, q_weight: torch.Tensor | None, k_weight: torch.Tensor | None,
+                           eps: float, slots: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, heads: int,
+                           kv_heads: int, dim: int, vdim: int, write_kv: bool = True, *, other_values=None,
+                           mix: torch.Tensor | None = None) -> torch.Tensor:
+        """Divide every q and k head of the float32 projection ``qkv`` [rows, heads*dim + kv_heads*dim +
+        kv_heads*vdim] by its root mean square over ``dim`` (times a weight [dim] where one is given), blend
+        the values with ``other_values`` (a float32 view [rows, kv_heads*vdim] with unit column stride):
+        v <- (1 - mix) v + mix * other, ``mix`` one float32 on the device; store k and v at ``slots`` of the
+        pools and return q [rows, heads*dim] in the pools' dtype."""
+        _need(qkv, "qkv", torch.float32, 2)
+        _need(slots, "slots", torch.int64, 1)
+        _need(k_pool, "k_pool", None, 4)
+        _need(v_pool, "v_pool", k_pool.dtype, 4)
+        rows = qkv.shape[0]
+        if qkv.shape[1] != (heads + kv_heads) * dim + kv_heads * vdim or slots.shape[0] != rows:
+            raise KernelError("qkv width does not match the head counts and sizes; one slot per row")
+        for name, vector in (("q_weight", q_weight), ("k_weight", k_weight)):
+            if vector is not None:
+                _need(vector, name, torch.float32, 1)
+                if vector.shape[0] != dim:
+                    raise KernelError(f"{name} holds {vector.shape[0]} entries, heads have {dim}")
+        if (k_pool.shape[1] != kv_heads or k_pool.shape[3] != dim or v_pool.shape[:3] != k_pool.shape[:3]
+                or v_pool.shape[3] != vdim):
+            raise KernelError(f"pools have shapes {tuple(k_pool.shape)} / {tuple(v_pool.shape)}, expected "
+                              f"[pages, {kv_heads}, page_size, {dim}] / [.., {vdim}]")
+        other = (ctypes.c_void_p(0), ctypes.c_longlong(0))
+        if other_values is not None:
+            other = self._view(other_values, "other_values", rows, kv_heads * vdim)
+            _need(mix, "mix", torch.float32)
+            if mix.numel() != 1:
+                raise KernelError("the blend is a single number")
+        q = torch.empty((rows, heads * dim), dtype=k_pool.dtype, device=qkv.device)
+        _check(build.load_library("attention_sigmoid").mlr_head_norm_kv_write(
+            _ptr(qkv), _ptr(q_weight), _ptr(k_weight), *other, _ptr(mix if other_values is not None else None),
+            _ptr(slots), _ptr(q), _ptr(k_pool), _ptr(v_pool), rows, heads, kv_heads, dim, vdim, k_pool.shape[2],
+            ctypes.c_float(eps), int(bool(write_kv)), _code(k_pool.dtype), _stream()), "head_norm_kv_write")
+        return q
+
+    SIGMOID_CHUNK_KEYS = 256      # keys one CTA of the sigmoid attention takes of a row, at least, when rows are few
+
+    def sigmoid_attention(self, q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, batch: AttentionBatch,
+                          heads: int, kv_heads: int, dim: int, vdim: int, scale: float, *, distance=None,
+                          score_bias: torch.Tensor | None = None, head_mix: torch.Tensor | None = None) -> torch.Tensor:
+        """Causal attention with un-normalised weights: w_g(i, j) = sigmoid(q_g(i) . k(j) * scale -
+        r1_g ln(1 + r2_g (i - j)) + score_bias_g) for j <= i (``distance`` = (r1, r2), float32 [heads] each, or
+        None), mixed across heads by ``head_mix`` [heads, heads] (w'_h = sum_g head_mix[h, g] w_g) when given;
+        head h applies its weights to the values of its own key/value head."""
+        _need(q, "q", dims=2)
+        _need(k_pool, "k_pool", q.dtype, 4)
+        _need(v_pool, "v_pool", q.dtype, 4)
+        if q.shape[1] != heads * dim or k_pool.shape[3] != dim or v_pool.shape[3] != vdim or k_pool.shape[1] != kv_heads:
+            raise KernelError("q, keys or values do not match the head counts and sizes")
+        if "tile_seg" not in batch.plan:
+            raise KernelError("the batch carries no attention work lists (plan_attention)")
+        r1, r2 = distance if distance is not None else (None, None)
+        for name, vector, shape in (("r1", r1, (heads,)), ("r2", r2, (heads,)), ("score_bias", score_bias, (heads,)),
+                                    ("head_mix", head_mix, (heads, heads))):
+            if vector is not None:
+                _need(vector, name, torch.float32)
+                if tuple(vector.shape) != shape:
+                    raise KernelError(f"{name} has shape {tuple(vector.shape)}, expected {shape}")
+        rows = q.shape[0]
+        out = torch.empty((rows, heads * vdim), dtype=q.dtype, device=q.device)
+        lib = build.load_library("attention_sigmoid")
+        per_cta = lib.mlr_attention_sigmoid_rows(heads, dim, vdim)
+        if per_cta <= 0:
+            raise KernelError("sigmoid attention: the heads are too many or too large for one CTA")
+        tiles = batch.counts["tiles"]
+        # steps of few rows: the keys of a row are shared out over several CTAs, about two CTAs per SM in all
+        ctas = tiles * (16 // per_cta)
+        want = max(1, 2 * self.sm_count(q.device) // max(ctas, 1))
+        chunks = max(1, min(want, -(-int(batch.max_kv_len) // self.SIGMOID_CHUNK_KEYS)))
+        chunk_keys = -(-(-(-int(batch.max_kv_len) // chunks)) // 32) * 32
+        partial = None
+        if chunks > 1:
+            partial = torch.empty((chunks, rows, heads * vdim), dtype=torch.float32, device=q.device)
+        _check(lib.mlr_attention_sigmoid(
+            _ptr(q), _ptr(k_pool), _ptr(v_pool), _ptr(out), _ptr(partial), _ptr(batch.plan["tile_seg"]),
+            _ptr(batch.plan["tile_row0"]), _ptr(batch.seg_q_start), _ptr(batch.seg_q_len), _ptr(batch.seg_pos0),
+            _ptr(batch.block_table), _ptr(batch.seg_slot), batch.block_table.shape[1], tiles, rows, heads, kv_heads, dim,
+            vdim, k_pool.shape[2], ctypes.c_float(scale), _ptr(r1), _ptr(r2), _ptr(score_bias), _ptr(head_mix), chunks,
+            max(chunk_keys, 32), _code(q.dtype), _stream()), "sigmoid attention")
+        return out
+
+    # ------------------------------------------------------------------ state-space mixer
+    def causal_conv(self, u: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | None, state: torch.Tensor, ctx,
+                    activation: str = "silu") -> torch.Tensor:
+        """Per channel and request: out[t] = act(bias + sum_k weight[:, k] * u[t - (taps - 1) + k]), the
+        inputs before the step's first token read from ``state`` [slots, taps - 1, channels] (the request's
+        last inputs, zeros at its start), which then receives the step's last inputs.  u: float32 view
+        [rows, channels] with unit column stride; returns float32 [rows, channels]."""
+        rows, channels = u.shape
+        _need(weight, "weight", torch.float32, 2)
+        taps = weight.shape[1]
+        if bias is not None:
+            _need(bias, "bias", torch.float32, 1)
+        _need(state, "state", torch.float32, 3)
+        if weight.shape[0] != channels or tuple(state.shape[1:]) != (taps - 1, channels) or (
+                bias is not None and bias.shape[0] != channels):
+            raise KernelError("causal_conv: weight [channels, taps], bias [channels], state [slots, taps - 1, channels]")
+        if activation not in ("silu", "none"):
+            raise KernelError(f"unknown activation {activation!r}")
+        out = torch.empty((rows, channels), dtype=torch.float32, device=u.device)
+        _check(build.load_library("state_space").mlr_causal_conv(
+            *self._view(u, "u", rows, channels), _ptr(weight), _ptr(bias), _ptr(state), _ptr(out), _ptr(ctx.seg_q_start),
+            _ptr(ctx.seg_q_len), _ptr(ctx.seg_slot), ctx.num_segments, int(ctx.max_q_len), channels, taps,
+            int(activation == "silu"), _stream()), "causal_conv")
+        return out
+
+    def state_space_scan(self, x, B, C, dt_raw, dt_bias, A_log, D, state, ctx, heads: int, vdim: int, n: int,
+                         groups: int) -> torch.Tensor:
+        """Per request and head h (group g = h // (heads / groups)), token by token: dt = softplus(dt_raw +
+        dt_bias), S <- exp(-exp(A_log) dt) S + dt B_g x_h^T, y_h = S^T C_g + D x_h.  x [rows, heads*vdim], B, C
+        [rows, groups*n], dt_raw [rows, heads]: float32 views with unit column stride; state: float32
+        [slots, heads, vdim, n] (the transposed S), advanced in place; returns float32 [rows, heads*vdim]."""
+        rows = x.shape[0]
+        for name, vector in (("dt_bias", dt_bias), ("A_log", A_log), ("D", D)):
+            _need(vector, name, torch.float32, 1)
+            if vector.shape[0] != heads:
+                raise KernelError(f"{name} needs one entry per head")
+        _need(state, "state", torch.float32, 4)
+        if tuple(state.shape[1:]) != (heads, vdim, n):
+            raise KernelError(f"state has shape {tuple(state.shape)}, expected [slots, {heads}, {vdim}, {n}]")
+        y = torch.empty((rows, heads * vdim), dtype=torch.float32, device=x.device)
+        _check(build.load_library("state_space").mlr_state_space_scan(
+            *self._view(x, "x", rows, heads * vdim), *self._view(B, "B", rows, groups * n),
+            *self._view(C, "C", rows, groups * n), *self._view(dt_raw, "dt_raw", rows, heads), _ptr(dt_bias), _ptr(A_log),
+            _ptr(D), _ptr(state), _ptr(y), _ptr(ctx.seg_q_start), _ptr(ctx.seg_q_len), _ptr(ctx.seg_slot),
+            ctx.num_segments, heads, vdim, n, groups, _stream()), "state_space_scan")
+        return y
+
+    def gated_group_norm(self, y: torch.Tensor, gate, weight: torch.Tensor, eps: float, parts: int,
+                         out_dtype: torch.dtype) -> torch.Tensor:
+        """(y * silu(gate)) cut into ``parts`` equal parts, each divided by its own root mean square, times
+        ``weight``.  y: float32 [rows, inner]; gate: a float32 view of that shape, or None for no gate."""
+        _need(y, "y", torch.float32, 2)
+        _need(weight, "weight", torch.float32, 1)
+        rows, inner = y.shape
+        if weight.shape[0] != inner or parts <= 0 or inner % parts:
+            raise KernelError("gated_group_norm: one weight per entry, and parts that divide the row")
+        gate_view = (ctypes.c_void_p(0), ctypes.c_longlong(0)) if gate is None else self._view(gate, "gate", rows, inner)
+        out = torch.empty((rows, inner), dtype=out_dtype, device=y.device)
+        _check(build.load_library("state_space").mlr_gated_group_norm(
+            _ptr(y), *gate_view, _ptr(weight), _ptr(out), rows, inner, int(parts), ctypes.c_float(eps), _code(out_dtype),
+            _stream()), "gated_group_norm")
         return out
 
     def sample(self, logits: torch.Tensor, temperatures: torch.Tensor, seeds: torch.Tensor,

@@ -308,6 +308,147 @@ class RotatedValueAttention(Mixer):
         return k.linear(mixed, self.w_o, out_dtype=torch.float32)
 
 
+class HeadNormAttention(Mixer):
+    """Grouped-query causal attention without a rotation, with q and k RMS-normalised per head.
+
+    q = Wq x + bq [heads * dim], k = Wk x + bk [kv_heads * dim], v = Wv x + bv [kv_heads * vdim] (one fused
+    product; ``bias=False``: no biases).  Every q and k head is divided by its root mean square over
+    ``dim`` (eps inside the root) and, with ``qk_norm_weight``, multiplied by a learned weight [dim] shared
+    by all heads (``q.norm``, ``k.norm``).  score = (q . k) * ``scale``; query head h reads key/value head
+    h // (heads / kv_heads); every j <= i is visible.  ``weights`` chooses what becomes of the scores:
+
+    * ``softmax``: the ordinary softmax over the visible keys;
+    * ``sigmoid``: w = sigmoid(score + b_h) for every visible key, not normalised over the keys.  The
+      optional pieces: ``distance_bias`` takes r1_h ln(1 + r2_h (i - j)) off the score (tensors ``r1``,
+      ``r2`` [heads]); ``score_bias`` is b (tensor ``pb`` [heads]); ``head_mix`` mixes the weights across
+      heads, w'_h = sum_g T[h, g] w_g (tensor ``talk`` [heads, heads]), before head h applies them to the
+      values of its own key/value head.
+
+    ``value_mix``: ``source`` hands this layer's values (as projected, 32-bit) to later layers of the same
+    step under the name ``value_mix_key``; ``blend`` replaces its own by (1 - m) v + m * those, m being the
+    tensor ``vmix`` (one number), before they are cached.  (A source layer's checkpoint carries ``vmix``
+    too; it is not used.)  Wo on the concatenated heads; the result leaves in 32-bit floats.
+
+    32-bit: the projections' results, the norms, the blend, scores and weights.  In bfloat16 the products'
+    operands, q, and the cached keys and values are bfloat16."""
+
+    graph_safe = True
+    plan_key = "paged_attention"
+
+    def __init__(self, spec, compute_dtype):
+        super().__init__(spec, compute_dtype)
+        a = self.args
+        self.hidden_size = int(a["hidden_size"])
+        self.heads = int(a["heads"])
+        self.kv_heads = int(a.get("kv_heads", self.heads))
+        self.dim = int(a["dim"])
+        self.vdim = int(a.get("vdim", self.dim))
+        self.scale = float(a["scale"])
+        self.eps = float(a["eps"])
+        self.bias = bool(a.get("bias", True))
+        self.qk_norm_weight = bool(a.get("qk_norm_weight", False))
+        self.weights = str(a.get("weights", "softmax"))
+        if self.weights not in ("softmax", "sigmoid"):
+            raise ValueError(f"unknown attention weights {self.weights!r}; known: softmax, sigmoid")
+        self.distance_bias = bool(a.get("distance_bias", False))
+        self.score_bias = bool(a.get("score_bias", False))
+        self.head_mix = bool(a.get("head_mix", False))
+        if self.weights == "softmax" and (self.distance_bias or self.score_bias or self.head_mix):
+            raise ValueError("distance bias, score bias and head mixing belong to sigmoid weights")
+        self.value_mix = a.get("value_mix")
+        if self.value_mix not in (None, "source", "blend"):
+            raise ValueError(f"unknown value_mix {self.value_mix!r}; known: source, blend")
+        self.value_mix_key = str(a.get("value_mix_key", "first_values"))
+        if self.heads % self.kv_heads:
+            raise ValueError("heads must be divisible by kv_heads")
+        self.w_qkv = self.b_qkv = self.w_o = self.q_norm = self.k_norm = None
+        self.r1 = self.r2 = self.pb = self.talk = self.mix = None
+
+    def cache_need(self):
+        return KVCacheNeed(self.kv_heads, self.dim, None, value_dim=None if self.vdim == self.dim else self.vdim)
+
+    def tensors(self):
+        p, h = self.prefix, self.hidden_size
+        sizes = {"q": self.heads * self.dim, "k": self.kv_heads * self.dim, "v": self.kv_heads * self.vdim}
+        out = {p + name: TensorSpec((rows, h)) for name, rows in sizes.items()}
+        if self.bias:
+            out.update({p + name + ".b": TensorSpec((rows,), init="bias") for name, rows in sizes.items()})
+        out[p + "o"] = TensorSpec((h, self.heads * self.vdim))
+        if self.qk_norm_weight:
+            out[p + "q.norm"] = TensorSpec((self.dim,), init="norm")
+            out[p + "k.norm"] = TensorSpec((self.dim,), init="norm")
+        if self.distance_bias:
+            out[p + "r1"] = TensorSpec((self.heads,), init="unit")
+            out[p + "r2"] = TensorSpec((self.heads,), init="unit")
+        if self.score_bias:
+            out[p + "pb"] = TensorSpec((self.heads,), init="bias")
+        if self.head_mix:
+            out[p + "talk"] = TensorSpec((self.heads, self.heads), init="matrix")
+        if self.value_mix is not None:
+            out[p + "vmix"] = TensorSpec((), init="unit")
+        return out
+
+    def load(self, tensors, device):
+        p = self.prefix
+
+        def f32(name):
+            return tensors[p + name].to(device=device, dtype=torch.float32).contiguous()
+
+        self.w_qkv = self._to_compute(torch.cat([tensors[p + n] for n in "qkv"], dim=0), device)
+        if self.bias:
+            self.b_qkv = self._to_compute(torch.cat([tensors[p + n + ".b"] for n in "qkv"], dim=0), device)
+        self.w_o = self._to_compute(tensors[p + "o"], device)
+        if self.qk_norm_weight:
+            self.q_norm, self.k_norm = f32("q.norm"), f32("k.norm")
+        if self.distance_bias:
+            self.r1, self.r2 = f32("r1"), f32("r2")
+        if self.score_bias:
+            self.pb = f32("pb")
+        if self.head_mix:
+            self.talk = f32("talk")
+        if self.value_mix == "blend":
+            self.mix = f32("vmix").reshape(1)
+
+    def step_plan(self, host):
+        return ops.current().plan_attention(host.lengths, host.position_start)
+
+    def _batch(self, ctx, view) -> AttentionBatch:
+        batch = view.shared.get("attention_batch")
+        if batch is None:
+            arrays, counts = ctx.plans.get(self.plan_key, ({}, {}))
+            batch = AttentionBatch(
+                seg_q_start=ctx.seg_q_start, seg_q_len=ctx.seg_q_len, seg_pos0=ctx.seg_pos0, seg_slot=ctx.seg_slot,
+                block_table=view.block_table, num_segments=ctx.num_segments, max_q_len=ctx.max_q_len,
+                max_kv_len=ctx.max_kv_len, plan=arrays, counts=counts)
+            view.shared["attention_batch"] = batch
+        return batch
+
+    def forward(self, x, ctx, view, writes_cache):
+        k = ops.current()
+        qkv = k.linear(x, self.w_qkv, self.b_qkv, out_dtype=torch.float32)
+        other = None
+        if self.value_mix == "source":
+            ctx.shared[self.value_mix_key] = qkv[:, (self.heads + self.kv_heads) * self.dim:]
+        elif self.value_mix == "blend":
+            other = ctx.shared.get(self.value_mix_key)
+            if other is None:
+                raise ValueError(f"no earlier layer of this step handed out {self.value_mix_key!r}")
+        q = k.head_norm_kv_write(qkv, self.q_norm, self.k_norm, self.eps, view.slots, view.k_pool, view.v_pool,
+                                 self.heads, self.kv_heads, self.dim, self.vdim, writes_cache, other_values=other,
+                                 mix=self.mix)
+        batch = self._batch(ctx, view)
+        if self.weights == "softmax":
+            mixed = k.paged_attention(q, view.k_pool, view.v_pool, batch, self.heads, self.kv_heads, self.dim,
+                                      self.scale, None, value_dim=self.vdim)
+        else:
+            mixed = k.sigmoid_attention(q, view.k_pool, view.v_pool, batch, self.heads, self.kv_heads, self.dim,
+                                        self.vdim, self.scale,
+                                        distance=(self.r1, self.r2) if self.distance_bias else None,
+                                        score_bias=self.pb, head_mix=self.talk)
+        return k.linear(mixed, self.w_o, out_dtype=torch.float32)
+
+
 register_part("mixer", "gqa_attention", GQAAttention)
+register_part("mixer", "head_norm_attention", HeadNormAttention)
 register_part("mixer", "differential_attention", DifferentialAttention)
 register_part("mixer", "rotated_value_attention", RotatedValueAttention)

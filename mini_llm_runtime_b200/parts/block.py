@@ -101,6 +101,44 @@ class SandwichNorm(Block):
         return residual, PendingDelta(passed, self.extras["feed_forward_post_norm"])
 
 
+class PostNormResidual(Block):
+    """Norms on the sublayers' outputs only: x <- x + norm1(mixer(x)), then x <- x + norm2(ff(x)); the
+    sublayers read the stream x itself (its rows in the compute dtype).  ``mixer_norm`` and
+    ``feed_forward_norm`` are those two norms (``StreamRMSNorm`` or any norm with ``add_into`` /
+    ``add_cast``).  The stream is 32-bit floats and the sublayers hand back 32-bit rows.  Each "add the
+    normalised output, hand the new stream to the next sublayer" is one pass over the stream: the layer's
+    last output travels on as a ``PendingDelta`` and is added by the next layer (or the model's final
+    norm).  A layer without a feed-forward ends after the first add."""
+
+    def _enter(self, residual, pending):
+        """Settle what the layer before left pending; returns the stream's rows in the compute dtype."""
+        dtype = self.mixer.compute_dtype
+        if isinstance(pending, PendingDelta) and pending.norm is not None and hasattr(pending.norm, "add_cast"):
+            return pending.norm.add_cast(residual, pending.tensor)
+        if pending is not None:
+            if isinstance(pending, PendingDelta):
+                if pending.norm is not None:
+                    pending.norm.add_into(residual, pending.tensor)
+                    pending = None
+                else:
+                    pending = pending.tensor
+            if pending is not None:
+                ops.current().add_residual(residual, pending)
+        if dtype == torch.float32:
+            return residual
+        return ops.current().rms_norm_step(residual, 0.0, out_dtype=dtype)
+
+    def forward(self, residual, pending, ctx, view, writes_cache):
+        rows = self._enter(residual, pending)
+        mixed = self.mixer.forward(rows, ctx, view, writes_cache)
+        if self.feed_forward is None:
+            return residual, PendingDelta(mixed, self.mixer_norm)
+        rows = self.mixer_norm.add_cast(residual, mixed)
+        passed = self.feed_forward.forward(rows, ctx)
+        return residual, PendingDelta(passed, self.feed_forward_norm)
+
+
 register_part("block", "pre_norm_residual", PreNormResidual)
+register_part("block", "post_norm_residual", PostNormResidual)
 register_part("block", "sandwich_norm", SandwichNorm)
 register_part("block", "parallel_shifted", ParallelShifted)

@@ -127,6 +127,60 @@ class LayerNorm(Norm):
                                              norm=self.pair, out_dtype=self.compute_dtype)
 
 
+class StreamRMSNorm(Norm):
+    """RMS norm for a 32-bit residual stream: y = v / sqrt(mean(v^2) + eps) * w, statistics and weight in
+    32-bit.  With ``one_plus`` the checkpoint stores the weight's offset from one: w = 1 + stored.  The
+    checkpoint name comes from the spec (``tensor``).  Uses, each one pass over the stream:
+
+    * ``forward(x)``: the normalised rows in the compute dtype;
+    * ``add_into(stream, delta)``: stream += norm(delta), for a norm that sits behind a sublayer;
+    * ``add_cast(stream, delta)``: the same, and the new rows of the stream in the compute dtype (the input
+      of a sublayer that reads the stream itself);
+    * ``add_forward(stream, delta, post=)``: stream += post(delta) (``post`` another norm of this kind; the
+      plain delta without one), then this norm of the new stream."""
+
+    graph_safe = True
+
+    def __init__(self, spec, compute_dtype):
+        super().__init__(spec, compute_dtype)
+        self.size = int(self.args["size"])
+        self.eps = float(self.args["eps"])
+        self.tensor = self.args.get("tensor") or self.prefix + "weight"
+        self.one_plus = bool(self.args.get("one_plus", False))
+        self.weight: torch.Tensor | None = None
+
+    def tensors(self):
+        return {self.tensor: TensorSpec((self.size,), init="bias" if self.one_plus else "norm")}
+
+    def load(self, tensors, device):
+        weight = tensors[self.tensor].to(device=device, dtype=torch.float32)
+        self.weight = (1.0 + weight if self.one_plus else weight).contiguous()
+
+    def forward(self, x):
+        return ops.current().rms_norm_step(x, self.eps, norm_weight=self.weight, out_dtype=self.compute_dtype)
+
+    def add_into(self, stream, delta):
+        ops.current().rms_norm_step(stream, self.eps, delta=delta, delta_weight=self.weight)
+        return stream
+
+    def add_cast(self, stream, delta):
+        if self.compute_dtype == torch.float32:
+            return self.add_into(stream, delta)
+        return ops.current().rms_norm_step(stream, self.eps, delta=delta, delta_weight=self.weight,
+                                           out_dtype=self.compute_dtype)
+
+    def add_forward(self, residual, delta, post=None):
+        if post is None:
+            ops.current().add_residual(residual, delta)
+            return self.forward(residual)
+        if post.eps != self.eps:
+            post.add_into(residual, delta)
+            return self.forward(residual)
+        return ops.current().rms_norm_step(residual, self.eps, delta=delta, delta_weight=post.weight,
+                                           norm_weight=self.weight, out_dtype=self.compute_dtype)
+
+
 register_part("norm", "rms_norm", RMSNorm)
+register_part("norm", "stream_rms_norm", StreamRMSNorm)
 register_part("norm", "layer_norm", LayerNorm)
 register_part("norm", "scalar_rms_norm", ScalarRMSNorm)

@@ -10,6 +10,8 @@ recurrence; the mixer's output projection leaves 32-bit rows for a 32-bit residu
            (coefficients ``mu.*``); w_t = exp(-exp(W2 tanh(W1 x_w) + w0));
            o_t = (S + diag(u) k_t v_t^T)^T r_t;  S <- diag(w_t) S + k_t v_t^T;
            out = Wo (o / rms(o) * norm * silu(Wg x_g)).
+``state_space``  a selective state-space layer with a scalar decay per head (Mamba-2, "state-space
+           duality"), see ``StateSpaceMixer``.
 ``hgrn2``  gated linear attention whose forget gate also sets what is written:
            f_t = l + (1 - l) sigmoid(Wf x + b);  S <- diag(f_t) S + (1 - f_t) v_t^T;
            o_t = S^T silu(Wq x);  out = Wo (o / rms(o) * norm).
@@ -132,5 +134,79 @@ class HGRN2Mixer(Mixer):
         return k.linear(mixed, self.w_o, out_dtype=torch.float32)
 
 
+class StateSpaceMixer(Mixer):
+    """Selective state-space layer with a scalar decay per head.
+
+    With inner = heads * vdim, N = ``state`` and G = ``groups``, one product W_in x yields
+    [z: inner | x: inner | B: G N | C: G N | dt: heads].  x, B and C together pass a causal convolution
+    per channel (``conv`` [channels, taps], last column the current token's, bias ``conv.b``, zeros before
+    the request's start) and silu.  dt <- softplus(dt + dt_bias).  Per head h, reading group
+    h // (heads / G):  S_t = exp(-exp(A_log_h) dt) S_(t-1) + dt B_t x_t^T  (S: N x vdim),
+    y_t = S_t^T C_t + D_h x_t.  Then y * silu(z), an RMS norm in ``norm_groups`` equal parts (each by its
+    own root mean square) times ``norm``, and W_o.
+
+    Per request the layer carries S (32-bit, kept transposed: [heads, vdim, N]) and the convolution's
+    last taps - 1 inputs.  Everything between the in-projection and W_o is 32-bit."""
+
+    graph_safe = True
+
+    def __init__(self, spec, compute_dtype):
+        super().__init__(spec, compute_dtype)
+        a = self.args
+        self.hidden_size = int(a["hidden_size"])
+        self.heads = int(a["heads"])
+        self.vdim = int(a["vdim"])
+        self.n = int(a["state"])
+        self.groups = int(a.get("groups", 1))
+        self.taps = int(a["conv"])
+        self.norm_groups = int(a.get("norm_groups", 1))
+        self.eps = float(a["eps"])
+        self.inner = self.heads * self.vdim
+        self.channels = self.inner + 2 * self.groups * self.n
+        if self.heads % self.groups or self.inner % self.norm_groups or self.taps < 2:
+            raise ValueError("heads must divide into the groups, the inner width into the norm's parts, and the "
+                             "convolution needs at least two taps")
+        self.w_in = self.w_o = self.conv = self.conv_bias = self.dt_bias = self.a_log = self.skip = self.norm = None
+
+    def cache_need(self):
+        return (StateNeed((self.heads, self.vdim, self.n), torch.float32, "state"),
+                StateNeed((self.taps - 1, self.channels), torch.float32, "conv"))
+
+    def tensors(self):
+        p, h = self.prefix, self.hidden_size
+        return {p + "in": TensorSpec((2 * self.inner + 2 * self.groups * self.n + self.heads, h)),
+                p + "conv": TensorSpec((self.channels, self.taps), init="bias"),
+                p + "conv.b": TensorSpec((self.channels,), init="bias"),
+                p + "dt_bias": TensorSpec((self.heads,), init="bias"),
+                p + "A_log": TensorSpec((self.heads,), init="bias"),
+                p + "D": TensorSpec((self.heads,), init="norm"),
+                p + "norm": TensorSpec((self.inner,), init="norm"),
+                p + "o": TensorSpec((h, self.inner))}
+
+    def load(self, tensors, device):
+        p = self.prefix
+        self.w_in = self._to_compute(tensors[p + "in"], device)
+        self.w_o = self._to_compute(tensors[p + "o"], device)
+        self.conv = _float(tensors[p + "conv"], device)
+        self.conv_bias = _float(tensors[p + "conv.b"], device)
+        self.dt_bias = _float(tensors[p + "dt_bias"], device)
+        self.a_log = _float(tensors[p + "A_log"], device)
+        self.skip = _float(tensors[p + "D"], device)
+        self.norm = _float(tensors[p + "norm"], device)
+
+    def forward(self, x, ctx, view, writes_cache):
+        k = ops.current()
+        inner, gn = self.inner, self.groups * self.n
+        projected = k.linear(x, self.w_in, out_dtype=torch.float32)
+        mixed = k.causal_conv(projected[:, inner:inner + self.channels], self.conv, self.conv_bias, view.states["conv"],
+                              ctx, "silu")
+        y = k.state_space_scan(mixed[:, :inner], mixed[:, inner:inner + gn], mixed[:, inner + gn:],
+                               projected[:, inner + self.channels:], self.dt_bias, self.a_log, self.skip,
+                               view.states["state"], ctx, self.heads, self.vdim, self.n, self.groups)
+        gated = k.gated_group_norm(y, projected[:, :inner], self.norm, self.eps, self.norm_groups, self.compute_dtype)
+        return k.linear(gated, self.w_o, out_dtype=torch.float32)
+
+
 register_part("mixer", "wkv", WKVMixer)
+register_part("mixer", "state_space", StateSpaceMixer)
 register_part("mixer", "hgrn2", HGRN2Mixer)

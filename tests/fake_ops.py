@@ -428,19 +428,20 @@ class FakeOps:
         x.copy_(turned.reshape(x.shape).to(x.dtype))
         return x
 
-    def route_experts(self, x, router, correction, top, groups=1, keep=1, scoring="softmax", renormalise=False):
+    def route_experts(self, x, router, correction, top, groups=1, keep=1, scoring="softmax", renormalise=False,
+                      group_top=1, renorm_eps=0.0):
         logits = x.float() @ router.T
         scores = torch.softmax(logits, dim=-1) if scoring == "softmax" else torch.sigmoid(logits)
         choice = scores if correction is None else scores + correction
         experts = router.shape[0]
         if keep < groups:
-            best = choice.view(-1, groups, experts // groups).max(dim=-1).values
+            best = choice.view(-1, groups, experts // groups).topk(min(group_top, experts // groups), dim=-1).values.sum(-1)
             kept = torch.zeros_like(best, dtype=torch.bool).scatter_(1, best.topk(keep, dim=-1).indices, True)
             choice = choice.masked_fill(~kept.repeat_interleave(experts // groups, dim=1), float("-inf"))
         chosen = choice.topk(top, dim=-1).indices
         weights = scores.gather(1, chosen)
         if renormalise:
-            weights = weights / weights.sum(-1, keepdim=True)
+            weights = weights / (weights.sum(-1, keepdim=True) + renorm_eps)
         return chosen.to(torch.int32), weights
 
     def routed_experts(self, x, chosen, weights, gate_up, down, block, activation="silu"):
@@ -451,3 +452,110 @@ class FakeOps:
                 hidden = self.gated_activation(self.linear(x[row:row + 1], gate_up[e]), block, activation)
                 out[row] += weights[row, t] * (hidden.float() @ down[e].float().T)[0]
         return out
+
+    # ---- 32-bit stream with RMS norms behind the sublayers
+    @staticmethod
+    def _rms(v, eps):
+        return v * torch.rsqrt((v * v).mean(-1, keepdim=True) + eps)
+
+    def rms_norm_step(self, x, eps, *, delta=None, delta_weight=None, norm_weight=None, out_dtype=None):
+        if delta is not None:
+            x += self._rms(delta, eps) * delta_weight
+        if out_dtype is None:
+            return None
+        return (x.clone() if norm_weight is None else self._rms(x, eps) * norm_weight).to(out_dtype)
+
+    def normed_mean(self, a, a_weight, b, b_weight, eps, factor):
+        return factor * (self._rms(a, eps) * a_weight + self._rms(b, eps) * b_weight)
+
+    # ---- plain-headed attention: prepare; sigmoid weights
+    def head_norm_kv_write(self, qkv, q_weight, k_weight, eps, slots, k_pool, v_pool, heads, kv_heads, dim, vdim,
+                           write_kv=True, *, other_values=None, mix=None):
+        rows, page_size = qkv.shape[0], k_pool.shape[2]
+        nq, nk = heads * dim, kv_heads * dim
+        q = self._rms(qkv[:, :nq].reshape(rows, heads, dim), eps)
+        k = self._rms(qkv[:, nq:nq + nk].reshape(rows, kv_heads, dim), eps)
+        if q_weight is not None:
+            q = q * q_weight
+        if k_weight is not None:
+            k = k * k_weight
+        v = qkv[:, nq + nk:]
+        if other_values is not None:
+            v = (1.0 - mix[0]) * v + mix[0] * other_values
+        v = v.reshape(rows, kv_heads, vdim)
+        if write_kv:
+            for t in range(rows):
+                slot = int(slots[t])
+                if slot < 0:
+                    continue
+                page, offset = divmod(slot, page_size)
+                k_pool[page, :, offset, :] = k[t].to(k_pool.dtype)
+                v_pool[page, :, offset, :] = v[t].to(v_pool.dtype)
+        return q.reshape(rows, nq).to(k_pool.dtype)
+
+    def sigmoid_attention(self, q, k_pool, v_pool, batch, heads, kv_heads, dim, vdim, scale, *, distance=None,
+                          score_bias=None, head_mix=None):
+        page_size = k_pool.shape[2]
+        group = heads // kv_heads
+        out = torch.empty((q.shape[0], heads * vdim), dtype=q.dtype)
+        q3 = q.float().view(-1, heads, dim)
+        for seg in range(batch.num_segments):
+            start, length, pos0 = int(batch.seg_q_start[seg]), int(batch.seg_q_len[seg]), int(batch.seg_pos0[seg])
+            table = batch.block_table[int(batch.seg_slot[seg])]
+            for r in range(length):
+                p = pos0 + r
+                keys = torch.arange(0, p + 1)
+                pages = table[(keys // page_size).long()].long()
+                assert (pages >= 0).all(), "attention reads a page the request does not hold"
+                offsets = (keys % page_size).long()
+                k = k_pool[pages, :, offsets, :].float().repeat_interleave(group, dim=1)
+                v = v_pool[pages, :, offsets, :].float().repeat_interleave(group, dim=1)
+                scores = torch.einsum("hd,khd->hk", q3[start + r], k) * scale
+                if distance is not None:
+                    r1, r2 = distance
+                    scores = scores - r1[:, None] * torch.log1p(r2[:, None] * (p - keys).float()[None, :])
+                if score_bias is not None:
+                    scores = scores + score_bias[:, None]
+                weights = torch.sigmoid(scores)
+                if head_mix is not None:
+                    weights = head_mix @ weights
+                out[start + r] = torch.einsum("hk,khd->hd", weights, v).reshape(-1).to(q.dtype)
+        return out
+
+    # ---- state-space mixer
+    def causal_conv(self, u, weight, bias, state, ctx, activation="silu"):
+        taps = weight.shape[1]
+        out = torch.empty(u.shape, dtype=torch.float32)
+        for segment in ctx.segments:
+            rows = slice(segment.row_start, segment.row_start + segment.length)
+            padded = torch.cat([state[segment.slot], u[rows]], dim=0)
+            total = torch.zeros((segment.length, u.shape[1]), dtype=torch.float32)
+            if bias is not None:
+                total = total + bias
+            for tap in range(taps):
+                total = total + padded[tap:tap + segment.length] * weight[:, tap]
+            out[rows] = torch.nn.functional.silu(total) if activation == "silu" else total
+            state[segment.slot] = padded[-(taps - 1):]
+        return out
+
+    def state_space_scan(self, x, B, C, dt_raw, dt_bias, A_log, D, state, ctx, heads, vdim, n, groups):
+        y = torch.empty((x.shape[0], heads * vdim), dtype=torch.float32)
+        dt = torch.nn.functional.softplus(dt_raw + dt_bias)
+        decay = torch.exp(-torch.exp(A_log) * dt)
+        per = heads // groups
+        for segment in ctx.segments:
+            S = state[segment.slot]                   # [heads, vdim, n]
+            for row in range(segment.row_start, segment.row_start + segment.length):
+                xr = x[row].view(heads, vdim)
+                Br = B[row].view(groups, n).repeat_interleave(per, dim=0)
+                Cr = C[row].view(groups, n).repeat_interleave(per, dim=0)
+                S = decay[row].view(heads, 1, 1) * S + dt[row].view(heads, 1, 1) * xr[:, :, None] * Br[:, None, :]
+                y[row] = (torch.einsum("hpn,hn->hp", S, Cr) + D[:, None] * xr).reshape(-1)
+            state[segment.slot] = S
+        return y
+
+    def gated_group_norm(self, y, gate, weight, eps, parts, out_dtype):
+        v = y if gate is None else y * torch.nn.functional.silu(gate)
+        rows, inner = v.shape
+        v = self._rms(v.reshape(rows, parts, inner // parts), eps).reshape(rows, inner)
+        return (v * weight).to(out_dtype)
