@@ -76,7 +76,7 @@ def parse_args():
     parser.add_argument("--gemm", default=None, metavar="M,N,K[,swiglu]",
                         help="time this engine's bfloat16 product x[M,K] W[N,K]^T on one shape (weights rotate over "
                              "copies larger than L2) and print a small JSON record; nothing else runs")
-    parser.add_argument("--arch", choices=("qwen2", "zazasun", "rozesun", "bopilorn"), default="qwen2",
+    parser.add_argument("--arch", choices=("qwen2", "zazasun", "rozesun", "bopilorn", "ratilorn"), default="qwen2",
                         help="zazasun: prefill and decode of the Zazasun architecture at a few layer sizes beside "
                              "Qwen2 at equal sizes, and its kernels alone against their rooflines (one JSON line "
                              "of its own; the default workload is untouched)")
@@ -766,6 +766,9 @@ def main():
     if args.arch == "bopilorn":
         import bench_bopilorn
         return bench_bopilorn.run(args, sys.modules[__name__])
+    if args.arch == "ratilorn":
+        import bench_ratilorn
+        return bench_ratilorn.run(args, sys.modules[__name__])
     return run_ours(args)
 
 

@@ -86,29 +86,56 @@ constexpr int KEYS = 32;          // keys per tile, one per lane
 constexpr int THREADS = 256;
 constexpr int PLAN_ROWS = 16;     // rows of one entry of the work list
 constexpr int MAX_ACC = 32;       // output sums a thread may hold
+constexpr int MAX_STAGE = 4;      // 16-byte pieces of the next tile a thread keeps in flight
 
 struct SigmoidArgs {
   const int *tile_seg, *tile_row0, *seg_q_start, *seg_q_len, *seg_pos0, *block_table, *seg_slot;
   const float *r1, *r2, *pb, *talk;
-  int table_width, heads, kv_heads, dim, vdim, page_size, rows_per_cta, chunk_keys, total_rows;
+  int table_width, heads, kv_heads, dim, vdim, page_size, rows_per_cta, chunk_keys, total_rows, tile_stride;
   float scale;
+};
+
+template <typename T> struct Piece;      // 16 bytes of a cached row as floats
+template <> struct Piece<float> {
+  static constexpr int N = 4;
+  static __device__ __forceinline__ void unpack(uint4 raw, float* dst) {
+    dst[0] = __uint_as_float(raw.x); dst[1] = __uint_as_float(raw.y);
+    dst[2] = __uint_as_float(raw.z); dst[3] = __uint_as_float(raw.w);
+  }
+};
+template <> struct Piece<bf16> {
+  static constexpr int N = 8;
+  static __device__ __forceinline__ void unpack(uint4 raw, float* dst) {
+    const uint32_t words[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      dst[2 * i] = __uint_as_float(words[i] << 16);
+      dst[2 * i + 1] = __uint_as_float(words[i] & 0xffff0000u);
+    }
+  }
 };
 
 // grid: (work-list entries, PLAN_ROWS / rows_per_cta, key chunks).  `partial` (float32 [chunks][rows]
 // [heads * vdim]) receives the sums when there are several chunks, else `out` does.
-template <typename T>
+//
+// A key tile passes through 2 * kv_heads phases: the keys of every key/value head (the heads' own
+// weights), the mixing, then the values of every key/value head.  Each phase's tile of 32 cached rows
+// goes through one shared buffer.  VECTOR (head sizes in whole 16-byte pieces): a thread asks for its
+// pieces of the NEXT phase's tile before it computes on this one, so the trip to memory runs under the
+// arithmetic; otherwise the tile is fetched entry by entry where it is needed.
+template <typename T, bool VECTOR>
 __global__ void __launch_bounds__(THREADS)
 attention_sigmoid_kernel(const T* q, const T* k_pool, const T* v_pool, T* out, float* partial, SigmoidArgs a) {
   pdl_trigger();
   extern __shared__ __align__(16) float shared[];
-  const int H = a.heads, G = a.kv_heads, D = a.dim, V = a.vdim, R = a.rows_per_cta;
+  const int H = a.heads, G = a.kv_heads, D = a.dim, V = a.vdim, R = a.rows_per_cta, ST = a.tile_stride;
   const int per_kv = H / G;
   float* q_rows = shared;                          // [H][R][D]
   float* w_raw = q_rows + (size_t)H * R * D;       // [H][R][KEYS]: the heads' own weights
   float* w_mix = w_raw + (size_t)H * R * KEYS;     // [H][R][KEYS]: mixed over the heads
-  float* k_tile = w_mix + (size_t)H * R * KEYS;    // [KEYS][D + 1]
-  float* v_tile = k_tile + KEYS * (D + 1);         // [KEYS][V]
-  float* talk = v_tile + KEYS * V;                 // [H][H]
+  float* tile = w_mix + (size_t)H * R * KEYS;      // [KEYS][ST]: this phase's keys or values
+  float* talk = tile + KEYS * ST;                  // [H][H]
+  int* key_row = reinterpret_cast<int*>(talk + H * H);      // [2][KEYS]: the cached row of every key of this and the next tile
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
 
   if (a.talk != nullptr)
@@ -134,87 +161,195 @@ attention_sigmoid_kernel(const T* q, const T* k_pool, const T* v_pool, T* out, f
 
   const int chunk_first = blockIdx.z * a.chunk_keys;
   const int chunk_last = min(last_pos, chunk_first + a.chunk_keys - 1);
-  for (int k0 = chunk_first; k0 <= chunk_last; k0 += KEYS) {
-    // ---- every head's own weights of this key tile
-    for (int c = 0; c < G; ++c) {
-      __syncthreads();
-      for (int idx = threadIdx.x; idx < KEYS * D; idx += THREADS) {
-        const int j = idx / D, d = idx - j * D;
-        const int key = k0 + j;
-        float kv = 0.f;
-        if (key <= last_pos) {
-          const int page = table[key / a.page_size];
-          if (page >= 0) kv = to_float(k_pool[(((size_t)page * G + c) * a.page_size + key % a.page_size) * D + d]);
-        }
-        k_tile[j * (D + 1) + d] = kv;
-      }
-      __syncthreads();
-      const float* kr = k_tile + lane * (D + 1);
+  const int phases = 2 * G;
+
+  // the cached row (without the head) of every key of the tile at k0: page * G * page_size + place in the page
+  auto find_rows = [&](int k0, int parity) {
+    if (warp == 0) {
       const int key = k0 + lane;
-      // (head of the group, row) pairs, two per warp and turn: one key entry feeds two sums
-      const int pairs = per_kv * rows;
-      for (int p = warp * 2; p < pairs; p += (THREADS / 32) * 2) {
-        const int ha = c * per_kv + p / rows, ra = p % rows;
-        const bool two = p + 1 < pairs;
-        const int hb = two ? c * per_kv + (p + 1) / rows : ha, rb = two ? (p + 1) % rows : ra;
-        const float* qa = q_rows + ((size_t)ha * R + ra) * D;
-        const float* qb = q_rows + ((size_t)hb * R + rb) * D;
-        float sa = 0.f, sb = 0.f;
-        for (int d = 0; d < D; ++d) {
-          const float kd = kr[d];
-          sa = fmaf(qa[d], kd, sa);
-          sb = fmaf(qb[d], kd, sb);
-        }
-        auto weight = [&](float s, int h, int r) -> float {
-          const int distance = first_pos + r - key;
-          if (distance < 0) return 0.f;
-          float z = s * a.scale;
-          if (a.r1 != nullptr) z -= a.r1[h] * log1pf(a.r2[h] * (float)distance);
-          if (a.pb != nullptr) z += a.pb[h];
-          return 1.f / (1.f + expf(-z));
-        };
-        w_raw[((size_t)ha * R + ra) * KEYS + lane] = weight(sa, ha, ra);
-        if (two) w_raw[((size_t)hb * R + rb) * KEYS + lane] = weight(sb, hb, rb);
+      int row = -1;
+      if (key <= last_pos) {
+        const int page = table[key / a.page_size];
+        if (page >= 0) row = page * G * a.page_size + key % a.page_size;
       }
+      key_row[parity * KEYS + lane] = row;
     }
-    __syncthreads();
-    // ---- the weights mixed across the heads
-    const float* w_use = w_raw;
-    if (a.talk != nullptr) {
-      for (int idx = threadIdx.x; idx < H * rows * KEYS; idx += THREADS) {
-        const int j = idx % KEYS, r = (idx / KEYS) % rows, h = idx / (KEYS * rows);
-        float sum = 0.f;
-        for (int g = 0; g < H; ++g) sum = fmaf(talk[h * H + g], w_raw[((size_t)g * R + r) * KEYS + j], sum);
-        w_mix[((size_t)h * R + r) * KEYS + j] = sum;
-      }
-      w_use = w_mix;
-    }
-    // ---- the values, one kv head at a time; output o = (h * R + r) * V + d belongs to thread o % THREADS
-    for (int c = 0; c < G; ++c) {
-      __syncthreads();
-      for (int idx = threadIdx.x; idx < KEYS * V; idx += THREADS) {
-        const int j = idx / V, d = idx - j * V;
-        const int key = k0 + j;
-        float vv = 0.f;
-        if (key <= last_pos) {
-          const int page = table[key / a.page_size];
-          if (page >= 0) vv = to_float(v_pool[(((size_t)page * G + c) * a.page_size + key % a.page_size) * V + d]);
-        }
-        v_tile[idx] = vv;
-      }
-      __syncthreads();
-      const int o_first = c * per_kv * R * V, o_end = (c + 1) * per_kv * R * V;
+  };
+  // VECTOR: this thread's pieces of the tile of `phase` (keys of head phase, or values of head phase - G)
+  uint4 stage[MAX_STAGE];
+  auto ask = [&](int phase, int parity) {
+    const bool values = phase >= G;
+    const int c = values ? phase - G : phase, W = values ? V : D;
+    const T* pool = values ? v_pool : k_pool;
+    const int per_row = W / Piece<T>::N;
 #pragma unroll
-      for (int i = 0; i < MAX_ACC; ++i) {
-        const int o = threadIdx.x + THREADS * i;
-        if (o >= o_first && o < o_end && o < outputs) {
-          const int d = o % V, hr = o / V;
-          if (hr % R < rows) {
-            const float* w = w_use + (size_t)hr * KEYS;
-            float sum = acc[i];
+    for (int l = 0; l < MAX_STAGE; ++l) {
+      const int e = threadIdx.x + THREADS * l;
+      stage[l] = make_uint4(0u, 0u, 0u, 0u);
+      if (e < KEYS * per_row) {
+        const int j = e / per_row, piece = e - j * per_row;
+        const int row = key_row[parity * KEYS + j];
+        if (row >= 0)
+          stage[l] = __ldcg(reinterpret_cast<const uint4*>(pool + ((size_t)row + (size_t)c * a.page_size) * W) + piece);
+      }
+    }
+  };
+  auto put = [&](int phase) {
+    const int W = phase >= G ? V : D;
+    const int per_row = W / Piece<T>::N;
+#pragma unroll
+    for (int l = 0; l < MAX_STAGE; ++l) {
+      const int e = threadIdx.x + THREADS * l;
+      if (e < KEYS * per_row) {
+        const int j = e / per_row, piece = e - j * per_row;
+        float values[Piece<T>::N];
+        Piece<T>::unpack(stage[l], values);
+        float* dst = tile + j * ST + piece * Piece<T>::N;
+#pragma unroll
+        for (int u = 0; u < Piece<T>::N; u += 4)
+          *reinterpret_cast<float4*>(dst + u) = make_float4(values[u], values[u + 1], values[u + 2], values[u + 3]);
+      }
+    }
+  };
+  auto fetch = [&](int phase, int parity) {      // the same, entry by entry
+    const bool values = phase >= G;
+    const int c = values ? phase - G : phase, W = values ? V : D;
+    const T* pool = values ? v_pool : k_pool;
+    for (int idx = threadIdx.x; idx < KEYS * W; idx += THREADS) {
+      const int j = idx / W, d = idx - j * W;
+      const int row = key_row[parity * KEYS + j];
+      tile[j * ST + d] = row >= 0 ? to_float(pool[((size_t)row + (size_t)c * a.page_size) * W + d]) : 0.f;
+    }
+  };
+
+  if (chunk_first <= chunk_last) {
+    find_rows(chunk_first, 0);
+    __syncthreads();
+    if (VECTOR) ask(0, 0);
+  }
+  int parity = 0;
+  for (int k0 = chunk_first; k0 <= chunk_last; k0 += KEYS, parity ^= 1) {
+    const bool more = k0 + KEYS <= chunk_last;
+    if (more) find_rows(k0 + KEYS, parity ^ 1);      // seen after the barriers below, long before it is used
+    for (int phase = 0; phase < phases; ++phase) {
+      __syncthreads();      // the phase before is done with the tile, and (phase G) all weights are written
+      if (phase == G && a.talk != nullptr) {
+        // ---- the weights mixed across the heads
+        for (int idx = threadIdx.x; idx < H * rows * KEYS; idx += THREADS) {
+          const int j = idx % KEYS, r = (idx / KEYS) % rows, h = idx / (KEYS * rows);
+          float sum = 0.f;
+          for (int g = 0; g < H; ++g) sum = fmaf(talk[h * H + g], w_raw[((size_t)g * R + r) * KEYS + j], sum);
+          w_mix[((size_t)h * R + r) * KEYS + j] = sum;
+        }
+      }
+      if (VECTOR) {
+        put(phase);
+        if (phase + 1 < phases) ask(phase + 1, parity);
+        else if (more) ask(0, parity ^ 1);
+      } else {
+        fetch(phase, parity);
+      }
+      __syncthreads();
+      if (phase < G) {
+        // ---- the own weights of the heads that read key head `phase`: (head, row) pairs, up to four per
+        // warp and turn (one key entry then feeds four sums), fewer when there are too few pairs for all warps
+        const int c = phase;
+        const float* kr = tile + lane * ST;
+        const int key = k0 + lane;
+        const int pairs = per_kv * rows;
+        const int per_turn = pairs >= 4 * (THREADS / 32) ? 4 : pairs >= 2 * (THREADS / 32) ? 2 : 1;
+        for (int p = warp * per_turn; p < pairs; p += (THREADS / 32) * per_turn) {
+          const float* qp[4];
+          int hh[4], rr[4];
+#pragma unroll
+          for (int u = 0; u < 4; ++u) {
+            const int pu = min(p + u, pairs - 1);
+            hh[u] = c * per_kv + pu / rows;
+            rr[u] = pu % rows;
+            qp[u] = q_rows + ((size_t)hh[u] * R + rr[u]) * D;
+          }
+          float s[4] = {0.f, 0.f, 0.f, 0.f};
+          if (VECTOR) {
+            for (int d = 0; d < D; d += 4) {
+              const float4 kd = *reinterpret_cast<const float4*>(kr + d);
+#pragma unroll
+              for (int u = 0; u < 4; ++u) {
+                if (u < per_turn) {
+                  const float4 qd = *reinterpret_cast<const float4*>(qp[u] + d);
+                  s[u] = fmaf(qd.x, kd.x, s[u]);
+                  s[u] = fmaf(qd.y, kd.y, s[u]);
+                  s[u] = fmaf(qd.z, kd.z, s[u]);
+                  s[u] = fmaf(qd.w, kd.w, s[u]);
+                }
+              }
+            }
+          } else {
+            for (int d = 0; d < D; ++d) {
+              const float kd = kr[d];
+#pragma unroll
+              for (int u = 0; u < 4; ++u)
+                if (u < per_turn) s[u] = fmaf(qp[u][d], kd, s[u]);
+            }
+          }
+#pragma unroll
+          for (int u = 0; u < 4; ++u) {
+            if (u >= per_turn || p + u >= pairs) break;
+            const int distance = first_pos + rr[u] - key;
+            float weight = 0.f;
+            if (distance >= 0) {
+              float z = s[u] * a.scale;
+              if (a.r1 != nullptr) z -= a.r1[hh[u]] * log1pf(a.r2[hh[u]] * (float)distance);
+              if (a.pb != nullptr) z += a.pb[hh[u]];
+              weight = 1.f / (1.f + expf(-z));
+            }
+            w_raw[((size_t)hh[u] * R + rr[u]) * KEYS + lane] = weight;
+          }
+        }
+      } else {
+        // ---- the values of key/value head c; output o = (h * R + r) * V + d belongs to thread o % THREADS
+        const int c = phase - G;
+        const float* w_use = a.talk != nullptr ? w_mix : w_raw;
+        const int o_first = c * per_kv * R * V, o_end = (c + 1) * per_kv * R * V;
+        if (THREADS % V == 0) {
+          // all of a thread's outputs share one value channel: its column of the tile stays in registers
+          const int d = threadIdx.x % V;
+          float column[KEYS];
+#pragma unroll
+          for (int j = 0; j < KEYS; ++j) column[j] = tile[j * ST + d];
+#pragma unroll
+          for (int i = 0; i < MAX_ACC; ++i) {
+            const int o = threadIdx.x + THREADS * i;
+            if (o >= o_first && o < o_end) {
+              const int hr = o / V;
+              if (hr % R < rows) {
+                const float4* w4 = reinterpret_cast<const float4*>(w_use + (size_t)hr * KEYS);
+                float sum = acc[i];
+#pragma unroll
+                for (int j4 = 0; j4 < KEYS / 4; ++j4) {
+                  const float4 w = w4[j4];
+                  sum = fmaf(w.x, column[4 * j4], sum);
+                  sum = fmaf(w.y, column[4 * j4 + 1], sum);
+                  sum = fmaf(w.z, column[4 * j4 + 2], sum);
+                  sum = fmaf(w.w, column[4 * j4 + 3], sum);
+                }
+                acc[i] = sum;
+              }
+            }
+          }
+        } else {
+#pragma unroll
+          for (int i = 0; i < MAX_ACC; ++i) {
+            const int o = threadIdx.x + THREADS * i;
+            if (o >= o_first && o < o_end) {
+              const int d = o % V, hr = o / V;
+              if (hr % R < rows) {
+                const float* w = w_use + (size_t)hr * KEYS;
+                float sum = acc[i];
 #pragma unroll 8
-            for (int j = 0; j < KEYS; ++j) sum = fmaf(w[j], v_tile[j * V + d], sum);
-            acc[i] = sum;
+                for (int j = 0; j < KEYS; ++j) sum = fmaf(w[j], tile[j * ST + d], sum);
+                acc[i] = sum;
+              }
+            }
           }
         }
       }
@@ -281,10 +416,19 @@ MLR_EXPORT int mlr_head_norm_kv_write(const float* qkv, const float* q_weight, c
   return launch_status();
 }
 
+// Floats between the rows of the shared tile: a multiple of four that is no multiple of eight (16-byte
+// pieces, and a quarter warp's pieces fall into different banks), or any odd number for single entries.
+static int sigmoid_tile_stride(int dim, int vdim, bool vector) {
+  const int widest = dim > vdim ? dim : vdim;
+  if (!vector) return widest | 1;
+  return widest % 8 == 0 ? widest + 4 : widest;
+}
+
 // Shared memory of one CTA that takes `rows` rows.
 static size_t sigmoid_shared_bytes(int heads, int dim, int vdim, int rows) {
-  return sizeof(float) * ((size_t)heads * rows * dim + 2 * (size_t)heads * rows * KEYS + (size_t)KEYS * (dim + 1) +
-                          (size_t)KEYS * vdim + (size_t)heads * heads);
+  const int widest = dim > vdim ? dim : vdim;
+  return sizeof(float) * ((size_t)heads * rows * dim + 2 * (size_t)heads * rows * KEYS + (size_t)KEYS * (widest + 4) +
+                          (size_t)heads * heads + 2 * KEYS);
 }
 
 // Rows per CTA (a power of two, at most 16) so that a thread holds at most MAX_ACC sums and the CTA's
@@ -316,8 +460,15 @@ MLR_EXPORT int mlr_attention_sigmoid(const void* q, const void* k_pool, const vo
     return MLR_BAD_SIZE;
   const int rows = mlr_attention_sigmoid_rows(heads, dim, vdim);
   if (rows == 0 || chunks > 65535) return MLR_TOO_LARGE;
+  // whole 16-byte pieces: head sizes in multiples of a piece, at most MAX_STAGE pieces per thread and tile
+  const int piece = dtype == MLR_BF16 ? 8 : 4;
+  const int widest = dim > vdim ? dim : vdim;
+  auto aligned = [](const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; };
+  const bool vector = dim % piece == 0 && vdim % piece == 0 && KEYS * (widest / piece) <= MAX_STAGE * THREADS &&
+                      aligned(k_pool) && aligned(v_pool);
   SigmoidArgs a{tile_seg, tile_row0, seg_q_start, seg_q_len, seg_pos0, block_table, seg_slot, r1, r2, pb, talk,
-                table_width, heads, kv_heads, dim, vdim, page_size, rows, chunk_keys, total_rows, scale};
+                table_width, heads, kv_heads, dim, vdim, page_size, rows, chunk_keys, total_rows,
+                sigmoid_tile_stride(dim, vdim, vector), scale};
   const size_t shared = sigmoid_shared_bytes(heads, dim, vdim, rows);
   const dim3 grid(tiles, PLAN_ROWS / rows, chunks);
   auto launch = [&](auto kernel, auto* typed_out) -> int {
@@ -335,7 +486,9 @@ MLR_EXPORT int mlr_attention_sigmoid(const void* q, const void* k_pool, const vo
                   typed_out, count, chunks);
     return launch_status();
   };
-  if (dtype == MLR_F32) return launch(attention_sigmoid_kernel<float>, (float*)out);
-  if (dtype == MLR_BF16) return launch(attention_sigmoid_kernel<bf16>, (bf16*)out);
+  if (dtype == MLR_F32)
+    return vector ? launch(attention_sigmoid_kernel<float, true>, (float*)out) : launch(attention_sigmoid_kernel<float, false>, (float*)out);
+  if (dtype == MLR_BF16)
+    return vector ? launch(attention_sigmoid_kernel<bf16, true>, (bf16*)out) : launch(attention_sigmoid_kernel<bf16, false>, (bf16*)out);
   return MLR_BAD_DTYPE;
 }

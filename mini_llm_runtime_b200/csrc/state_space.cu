@@ -104,21 +104,31 @@ struct ScanArgs {
   int heads, vdim, n, groups;
 };
 
+// Asynchronous copies into shared memory (the data never passes through registers, and the thread goes on).
+__device__ __forceinline__ void copy_async_4(float* dst, const float* src) {
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"((uint32_t)__cvta_generic_to_shared(dst)), "l"(src) : "memory");
+}
+__device__ __forceinline__ void copy_async_16(float* dst, const float* src) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((uint32_t)__cvta_generic_to_shared(dst)), "l"(src) : "memory");
+}
+__device__ __forceinline__ void copy_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N> __device__ __forceinline__ void copy_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+
 // SL: threads that share one value channel's state (a power of two; SL * SCAN_NPT >= n).  Lane l of a warp
 // holds entries [s * 16, s * 16 + 16) of channel p with s = l % SL, p = l / SL.
-// grid: (segments, heads, value-channel blocks).
-template <int SL>
+// grid: (segments, heads, value-channel blocks).  The inputs of 32 tokens at a time are staged in shared
+// memory by asynchronous copies, the next 32 while these are walked; WIDE: in 16-byte pieces (state size,
+// channel block and all row strides multiples of four floats, pointers aligned).
+template <int SL, bool WIDE>
 __global__ void __launch_bounds__(SCAN_THREADS)
 state_space_scan_kernel(ScanArgs a) {
   pdl_trigger();
   extern __shared__ __align__(16) float shared[];
   constexpr int P_CTA = SCAN_THREADS / SL;
   const int N = a.n, P = a.vdim;
-  float* b_rows = shared;                             // [SCAN_TOKENS][N], already times dt
-  float* c_rows = b_rows + SCAN_TOKENS * N;           // [SCAN_TOKENS][N]
-  float* x_rows = c_rows + SCAN_TOKENS * N;           // [SCAN_TOKENS][P_CTA]
-  float* decay = x_rows + SCAN_TOKENS * P_CTA;        // [SCAN_TOKENS]
-  float* step = decay + SCAN_TOKENS;                  // [SCAN_TOKENS]
+  const int buffer = SCAN_TOKENS * (2 * N + P_CTA + 1);      // floats of one staging buffer
+  float* decay = shared + 2 * buffer + SCAN_NPT;             // [SCAN_TOKENS]; a last piece may reach past a buffer's end
+  float* step = decay + SCAN_TOKENS;                         // [SCAN_TOKENS]
   const int seg = blockIdx.x, head = blockIdx.y;
   const int group = head / (a.heads / a.groups);
   const int s = threadIdx.x % SL, p_local = threadIdx.x / SL;
@@ -126,6 +136,46 @@ state_space_scan_kernel(ScanArgs a) {
   const float rate = expf(a.A_log[head]), bias = a.dt_bias[head], skip = a.D[head];
   pdl_wait();
   const int q_start = a.seg_q_start[seg], q_len = a.seg_q_len[seg];
+
+  // rows [t0, t0 + 32) of the segment into buffer `which`: B and C of the head's group, the block's value
+  // channels of x, the head's raw step sizes
+  auto stage = [&](int t0, int which) {
+    float* b_rows = shared + which * buffer;
+    float* c_rows = b_rows + SCAN_TOKENS * N;
+    float* x_rows = c_rows + SCAN_TOKENS * N;
+    float* raw = x_rows + SCAN_TOKENS * P_CTA;
+    const int tokens = min(SCAN_TOKENS, q_len - t0);
+    const size_t row0 = (size_t)(q_start + t0);
+    if (WIDE) {
+      const int per_row = N >> 2;
+      for (int idx = threadIdx.x; idx < tokens * per_row; idx += SCAN_THREADS) {
+        const int t = idx / per_row, n = (idx - t * per_row) << 2;
+        copy_async_16(b_rows + t * N + n, a.B + (row0 + t) * a.b_stride + (size_t)group * N + n);
+        copy_async_16(c_rows + t * N + n, a.C + (row0 + t) * a.c_stride + (size_t)group * N + n);
+      }
+      constexpr int X_PIECES = P_CTA / 4;
+      for (int idx = threadIdx.x; idx < tokens * X_PIECES; idx += SCAN_THREADS) {
+        const int t = idx / X_PIECES, pl = (idx - t * X_PIECES) << 2;
+        const int pp = blockIdx.z * P_CTA + pl;
+        if (pp < P) copy_async_16(x_rows + t * P_CTA + pl, a.x + (row0 + t) * a.x_stride + (size_t)head * P + pp);
+      }
+    } else {
+      for (int idx = threadIdx.x; idx < tokens * N; idx += SCAN_THREADS) {
+        const int t = idx / N, n = idx - t * N;
+        copy_async_4(b_rows + idx, a.B + (row0 + t) * a.b_stride + (size_t)group * N + n);
+        copy_async_4(c_rows + idx, a.C + (row0 + t) * a.c_stride + (size_t)group * N + n);
+      }
+      for (int idx = threadIdx.x; idx < tokens * P_CTA; idx += SCAN_THREADS) {
+        const int t = idx / P_CTA, pl = idx - t * P_CTA;
+        const int pp = blockIdx.z * P_CTA + pl;
+        if (pp < P) copy_async_4(x_rows + idx, a.x + (row0 + t) * a.x_stride + (size_t)head * P + pp);
+      }
+    }
+    if (threadIdx.x < tokens) copy_async_4(raw + threadIdx.x, a.dt_raw + (row0 + threadIdx.x) * a.dt_stride + head);
+    copy_async_commit();
+  };
+
+  stage(0, 0);
   float* state = a.states + (((size_t)a.seg_slot[seg] * a.heads + head) * P + (p < P ? p : 0)) * N;
   float S[SCAN_NPT];
 #pragma unroll
@@ -133,44 +183,59 @@ state_space_scan_kernel(ScanArgs a) {
     const int n = s * SCAN_NPT + i;
     S[i] = (p < P && n < N) ? state[n] : 0.f;
   }
-  for (int t0 = 0; t0 < q_len; t0 += SCAN_TOKENS) {
+  int which = 0;
+  for (int t0 = 0; t0 < q_len; t0 += SCAN_TOKENS, which ^= 1) {
     const int tokens = min(SCAN_TOKENS, q_len - t0);
+    const bool more = t0 + SCAN_TOKENS < q_len;
+    if (more) stage(t0 + SCAN_TOKENS, which ^ 1);
+    if (more) copy_async_wait<1>(); else copy_async_wait<0>();
     __syncthreads();
+    const float* b_rows = shared + which * buffer;
+    const float* c_rows = b_rows + SCAN_TOKENS * N;
+    const float* x_rows = c_rows + SCAN_TOKENS * N;
+    const float* raw = x_rows + SCAN_TOKENS * P_CTA;
     if (threadIdx.x < tokens) {
-      const float raw = __ldcg(a.dt_raw + (size_t)(q_start + t0 + threadIdx.x) * a.dt_stride + head) + bias;
-      const float dt = raw > 20.f ? raw : log1pf(expf(raw));
+      const float z = raw[threadIdx.x] + bias;
+      const float dt = z > 20.f ? z : log1pf(expf(z));
       step[threadIdx.x] = dt;
       decay[threadIdx.x] = expf(-rate * dt);
     }
     __syncthreads();
-    for (int idx = threadIdx.x; idx < tokens * N; idx += SCAN_THREADS) {
-      const int t = idx / N, n = idx - t * N;
-      const size_t row = (size_t)(q_start + t0 + t);
-      b_rows[idx] = __ldcg(a.B + row * a.b_stride + (size_t)group * N + n) * step[t];
-      c_rows[idx] = __ldcg(a.C + row * a.c_stride + (size_t)group * N + n);
-    }
-    for (int idx = threadIdx.x; idx < tokens * P_CTA; idx += SCAN_THREADS) {
-      const int t = idx / P_CTA, pl = idx - t * P_CTA;
-      const int pp = blockIdx.z * P_CTA + pl;
-      x_rows[idx] = pp < P ? __ldcg(a.x + (size_t)(q_start + t0 + t) * a.x_stride + (size_t)head * P + pp) : 0.f;
-    }
-    __syncthreads();
     for (int t = 0; t < tokens; ++t) {
-      const float av = decay[t], xv = x_rows[t * P_CTA + p_local];
+      const float av = decay[t], xv = p < P ? x_rows[t * P_CTA + p_local] : 0.f;
+      const float dx = step[t] * xv;
       const float* bt = b_rows + t * N + s * SCAN_NPT;
       const float* ct = c_rows + t * N + s * SCAN_NPT;
-      float sum = 0.f;
+      float bv[SCAN_NPT], cv[SCAN_NPT];
+      if (WIDE) {
+#pragma unroll
+        for (int i = 0; i < SCAN_NPT; i += 4) {
+          const float4 b4 = *reinterpret_cast<const float4*>(bt + i), c4 = *reinterpret_cast<const float4*>(ct + i);
+          bv[i] = b4.x; bv[i + 1] = b4.y; bv[i + 2] = b4.z; bv[i + 3] = b4.w;
+          cv[i] = c4.x; cv[i + 1] = c4.y; cv[i + 2] = c4.z; cv[i + 3] = c4.w;
+        }
+      } else {
+#pragma unroll
+        for (int i = 0; i < SCAN_NPT; ++i) {
+          const bool in = s * SCAN_NPT + i < N;
+          bv[i] = in ? bt[i] : 0.f;
+          cv[i] = in ? ct[i] : 0.f;
+        }
+      }
+      float sums[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
       for (int i = 0; i < SCAN_NPT; ++i) {
         if (s * SCAN_NPT + i < N) {
-          S[i] = fmaf(av, S[i], bt[i] * xv);
-          sum = fmaf(S[i], ct[i], sum);
+          S[i] = fmaf(av, S[i], bv[i] * dx);
+          sums[i & 3] = fmaf(S[i], cv[i], sums[i & 3]);
         }
       }
+      float sum = (sums[0] + sums[1]) + (sums[2] + sums[3]);
 #pragma unroll
       for (int offset = SL / 2; offset > 0; offset >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, offset);
       if (s == 0 && p < P) a.y[(size_t)(q_start + t0 + t) * a.heads * P + (size_t)head * P + p] = fmaf(skip, xv, sum);
     }
+    __syncthreads();      // the next round stages into this buffer
   }
   if (p < P) {
 #pragma unroll
@@ -244,9 +309,13 @@ MLR_EXPORT int mlr_state_space_scan(const float* x, long long x_stride, const fl
              seg_q_start, seg_q_len, seg_slot, heads, vdim, n, groups};
   int slices = 1;
   while (slices * SCAN_NPT < n) slices *= 2;
+  auto multiple = [](long long v) { return v % 4 == 0; };
+  auto aligned = [](const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; };
+  const bool wide = multiple(n) && multiple(vdim) && multiple(x_stride) && multiple(b_stride) && multiple(c_stride) &&
+                    aligned(x) && aligned(B) && aligned(C);
   auto launch = [&](auto kernel, int sl) -> int {
     const int p_cta = SCAN_THREADS / sl;
-    const size_t shared = sizeof(float) * ((size_t)SCAN_TOKENS * (2 * n + p_cta) + 2 * SCAN_TOKENS);
+    const size_t shared = sizeof(float) * (2 * (size_t)SCAN_TOKENS * (2 * n + p_cta + 1) + SCAN_NPT + 2 * SCAN_TOKENS);
     if (shared > 48 * 1024) {
       cudaError_t err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)shared);
       if (err != cudaSuccess) return (int)err;
@@ -255,12 +324,12 @@ MLR_EXPORT int mlr_state_space_scan(const float* x, long long x_stride, const fl
     return launch_status();
   };
   switch (slices) {
-    case 1: return launch(state_space_scan_kernel<1>, 1);
-    case 2: return launch(state_space_scan_kernel<2>, 2);
-    case 4: return launch(state_space_scan_kernel<4>, 4);
-    case 8: return launch(state_space_scan_kernel<8>, 8);
-    case 16: return launch(state_space_scan_kernel<16>, 16);
-    default: return launch(state_space_scan_kernel<32>, 32);
+    case 1: return wide ? launch(state_space_scan_kernel<1, true>, 1) : launch(state_space_scan_kernel<1, false>, 1);
+    case 2: return wide ? launch(state_space_scan_kernel<2, true>, 2) : launch(state_space_scan_kernel<2, false>, 2);
+    case 4: return wide ? launch(state_space_scan_kernel<4, true>, 4) : launch(state_space_scan_kernel<4, false>, 4);
+    case 8: return wide ? launch(state_space_scan_kernel<8, true>, 8) : launch(state_space_scan_kernel<8, false>, 8);
+    case 16: return wide ? launch(state_space_scan_kernel<16, true>, 16) : launch(state_space_scan_kernel<16, false>, 16);
+    default: return wide ? launch(state_space_scan_kernel<32, true>, 32) : launch(state_space_scan_kernel<32, false>, 32);
   }
 }
 

@@ -356,6 +356,106 @@ normed_mean_kernel(const float* a, const float* __restrict__ wa, const float* b,
     out[base + d] = factor * (staged[d] * ra * wa[d] + second[d] * rb * wb[d]);
 }
 
+// The same two for steps of few rows (decoding): one CTA of THREADS threads per row, at most four float4
+// pieces per thread, every operand asked for before the first is used (one trip to memory).
+template <typename T, int THREADS>
+__global__ void __launch_bounds__(THREADS)
+rms_norm_step_row_kernel(float* x, const float* delta, const float* __restrict__ dw, const float* __restrict__ w,
+                         T* __restrict__ out, int width, float eps) {
+  pdl_trigger();
+  __shared__ float scratch[THREADS / 32];
+  constexpr int CH = 4;
+  const int pieces = width >> 2;
+  const size_t base = (size_t)blockIdx.x * width;
+  const float4 zero = make_float4(0.f, 0.f, 0.f, 0.f);
+  float4 dwv[CH], wv[CH], dv[CH], xv[CH];
+#pragma unroll
+  for (int j = 0; j < CH; ++j) {
+    const int c = threadIdx.x + THREADS * j;
+    const bool in = c < pieces;
+    dwv[j] = in && delta != nullptr ? reinterpret_cast<const float4*>(dw)[c] : zero;
+    wv[j] = in && out != nullptr && w != nullptr ? reinterpret_cast<const float4*>(w)[c] : zero;
+  }
+  pdl_wait();
+#pragma unroll
+  for (int j = 0; j < CH; ++j) {
+    const int c = threadIdx.x + THREADS * j;
+    const bool in = c < pieces;
+    dv[j] = in && delta != nullptr ? __ldcg(reinterpret_cast<const float4*>(delta + base) + c) : zero;
+    xv[j] = in ? __ldcg(reinterpret_cast<const float4*>(x + base) + c) : zero;
+  }
+  if (delta != nullptr) {
+    float sq = 0.f;
+#pragma unroll
+    for (int j = 0; j < CH; ++j) sq += fmaf(dv[j].x, dv[j].x, dv[j].y * dv[j].y) + fmaf(dv[j].z, dv[j].z, dv[j].w * dv[j].w);
+    const float rstd = 1.f / sqrtf(block_sum_of<THREADS>(sq, scratch) / (float)width + eps);
+#pragma unroll
+    for (int j = 0; j < CH; ++j) {
+      xv[j].x += dv[j].x * rstd * dwv[j].x; xv[j].y += dv[j].y * rstd * dwv[j].y;
+      xv[j].z += dv[j].z * rstd * dwv[j].z; xv[j].w += dv[j].w * rstd * dwv[j].w;
+      if (threadIdx.x + THREADS * j < pieces) store4(x + base + 4 * (threadIdx.x + THREADS * j), xv[j]);
+    }
+  }
+  if (out == nullptr) return;
+  float rstd = 1.f;
+  if (w != nullptr) {
+    float sq = 0.f;
+#pragma unroll
+    for (int j = 0; j < CH; ++j) sq += fmaf(xv[j].x, xv[j].x, xv[j].y * xv[j].y) + fmaf(xv[j].z, xv[j].z, xv[j].w * xv[j].w);
+    rstd = 1.f / sqrtf(block_sum_of<THREADS>(sq, scratch) / (float)width + eps);
+  }
+#pragma unroll
+  for (int j = 0; j < CH; ++j) {
+    if (threadIdx.x + THREADS * j >= pieces) continue;
+    float4 o = xv[j];
+    if (w != nullptr) o = make_float4(o.x * rstd * wv[j].x, o.y * rstd * wv[j].y, o.z * rstd * wv[j].z, o.w * rstd * wv[j].w);
+    store4(out + base + 4 * (threadIdx.x + THREADS * j), o);
+  }
+}
+
+template <int THREADS>
+__global__ void __launch_bounds__(THREADS)
+normed_mean_row_kernel(const float* a, const float* __restrict__ wa, const float* b, const float* __restrict__ wb,
+                       float* __restrict__ out, int width, float eps, float factor) {
+  pdl_trigger();
+  __shared__ float scratch[THREADS / 32];
+  constexpr int CH = 4;
+  const int pieces = width >> 2;
+  const size_t base = (size_t)blockIdx.x * width;
+  const float4 zero = make_float4(0.f, 0.f, 0.f, 0.f);
+  float4 wav[CH], wbv[CH], av[CH], bv[CH];
+#pragma unroll
+  for (int j = 0; j < CH; ++j) {
+    const int c = threadIdx.x + THREADS * j;
+    wav[j] = c < pieces ? reinterpret_cast<const float4*>(wa)[c] : zero;
+    wbv[j] = c < pieces ? reinterpret_cast<const float4*>(wb)[c] : zero;
+  }
+  pdl_wait();
+#pragma unroll
+  for (int j = 0; j < CH; ++j) {
+    const int c = threadIdx.x + THREADS * j;
+    av[j] = c < pieces ? __ldcg(reinterpret_cast<const float4*>(a + base) + c) : zero;
+    bv[j] = c < pieces ? __ldcg(reinterpret_cast<const float4*>(b + base) + c) : zero;
+  }
+  float sa = 0.f, sb = 0.f;
+#pragma unroll
+  for (int j = 0; j < CH; ++j) {
+    sa += fmaf(av[j].x, av[j].x, av[j].y * av[j].y) + fmaf(av[j].z, av[j].z, av[j].w * av[j].w);
+    sb += fmaf(bv[j].x, bv[j].x, bv[j].y * bv[j].y) + fmaf(bv[j].z, bv[j].z, bv[j].w * bv[j].w);
+  }
+  const float ra = 1.f / sqrtf(block_sum_of<THREADS>(sa, scratch) / (float)width + eps);
+  const float rb = 1.f / sqrtf(block_sum_of<THREADS>(sb, scratch) / (float)width + eps);
+#pragma unroll
+  for (int j = 0; j < CH; ++j) {
+    const int c = threadIdx.x + THREADS * j;
+    if (c >= pieces) continue;
+    store4(out + base + 4 * c, make_float4(factor * (av[j].x * ra * wav[j].x + bv[j].x * rb * wbv[j].x),
+                                           factor * (av[j].y * ra * wav[j].y + bv[j].y * rb * wbv[j].y),
+                                           factor * (av[j].z * ra * wav[j].z + bv[j].z * rb * wbv[j].z),
+                                           factor * (av[j].w * ra * wav[j].w + bv[j].w * rb * wbv[j].w)));
+  }
+}
+
 template <typename T>
 __global__ void __launch_bounds__(256)
 clamped_gate_kernel(const T* x, T* __restrict__ out, long long rows, int inner, int block, float limit, float slope) {
@@ -474,7 +574,20 @@ MLR_EXPORT int mlr_rms_norm_step(float* x, const float* delta, const float* dw, 
   if (rows < 0 || width <= 0 || (delta != nullptr && dw == nullptr)) return MLR_BAD_SIZE;
   const size_t shared = sizeof(float) * ((size_t)width + 32);
   if (shared > 200 * 1024) return MLR_TOO_LARGE;
+  auto aligned = [](const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; };
+  const bool few = rows <= 64 && width % 4 == 0 && width <= 8192 && aligned(x) && aligned(delta) && aligned(dw) && aligned(w) &&
+                   aligned(out);
   auto launch = [&](auto kernel, auto* typed_out) -> int {
+    using T = std::remove_pointer_t<decltype(typed_out)>;
+    if (few) {
+      if (width <= 2048)
+        launch_kernel(rms_norm_step_row_kernel<T, 128>, dim3(rows), dim3(128), 0, stream, x, delta, dw, w, typed_out, width, eps);
+      else if (width <= 4096)
+        launch_kernel(rms_norm_step_row_kernel<T, 256>, dim3(rows), dim3(256), 0, stream, x, delta, dw, w, typed_out, width, eps);
+      else
+        launch_kernel(rms_norm_step_row_kernel<T, 512>, dim3(rows), dim3(512), 0, stream, x, delta, dw, w, typed_out, width, eps);
+      return launch_status();
+    }
     if (shared > 48 * 1024) {
       cudaError_t err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)shared);
       if (err != cudaSuccess) return (int)err;
@@ -494,6 +607,16 @@ MLR_EXPORT int mlr_normed_mean(const float* a, const float* wa, const float* b, 
   if (rows < 0 || width <= 0) return MLR_BAD_SIZE;
   const size_t shared = sizeof(float) * (2 * (size_t)width + 32);
   if (shared > 200 * 1024) return MLR_TOO_LARGE;
+  auto aligned = [](const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; };
+  if (rows <= 64 && width % 4 == 0 && width <= 8192 && aligned(a) && aligned(wa) && aligned(b) && aligned(wb) && aligned(out)) {
+    if (width <= 2048)
+      launch_kernel(normed_mean_row_kernel<128>, dim3(rows), dim3(128), 0, stream, a, wa, b, wb, out, width, eps, factor);
+    else if (width <= 4096)
+      launch_kernel(normed_mean_row_kernel<256>, dim3(rows), dim3(256), 0, stream, a, wa, b, wb, out, width, eps, factor);
+    else
+      launch_kernel(normed_mean_row_kernel<512>, dim3(rows), dim3(512), 0, stream, a, wa, b, wb, out, width, eps, factor);
+    return launch_status();
+  }
   if (shared > 48 * 1024) {
     cudaError_t err = cudaFuncSetAttribute(normed_mean_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)shared);
     if (err != cudaSuccess) return (int)err;

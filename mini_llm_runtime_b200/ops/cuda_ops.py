@@ -1489,7 +1489,7 @@ class CudaOps:
             ctypes.c_float(eps), int(bool(write_kv)), _code(k_pool.dtype), _stream()), "head_norm_kv_write")
         return q
 
-    SIGMOID_CHUNK_KEYS = 256      # keys one CTA of the sigmoid attention takes of a row, at least, when rows are few
+    SIGMOID_CHUNK_KEYS = 64       # keys one CTA of the sigmoid attention takes of a row, at least, when rows are few
 
     def sigmoid_attention(self, q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, batch: AttentionBatch,
                           heads: int, kv_heads: int, dim: int, vdim: int, scale: float, *, distance=None,
@@ -1519,9 +1519,10 @@ class CudaOps:
         if per_cta <= 0:
             raise KernelError("sigmoid attention: the heads are too many or too large for one CTA")
         tiles = batch.counts["tiles"]
-        # steps of few rows: the keys of a row are shared out over several CTAs, about two CTAs per SM in all
-        ctas = tiles * (16 // per_cta)
-        want = max(1, 2 * self.sm_count(q.device) // max(ctas, 1))
+        # steps of few rows: the keys of a row are shared out over several CTAs, about three CTAs per SM in all
+        # (a one-row segment's entry keeps one CTA busy, another entry 16 / per_cta of them)
+        ctas = batch.num_decode + (tiles - batch.num_decode) * (16 // per_cta)
+        want = max(1, 3 * self.sm_count(q.device) // max(ctas, 1))
         chunks = max(1, min(want, -(-int(batch.max_kv_len) // self.SIGMOID_CHUNK_KEYS)))
         chunk_keys = -(-(-(-int(batch.max_kv_len) // chunks)) // 32) * 32
         partial = None
