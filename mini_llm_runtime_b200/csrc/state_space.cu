@@ -235,7 +235,7 @@ state_space_scan_kernel(ScanArgs a) {
       for (int offset = SL / 2; offset > 0; offset >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, offset);
       if (s == 0 && p < P) a.y[(size_t)(q_start + t0 + t) * a.heads * P + (size_t)head * P + p] = fmaf(skip, xv, sum);
     }
-    __syncthreads();      // the next round stages into this buffer
+    __syncthreads();      // the next turn of the loop stages into this buffer
   }
   if (p < P) {
 #pragma unroll

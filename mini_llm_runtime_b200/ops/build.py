@@ -51,6 +51,7 @@ LIBRARIES: dict[str, tuple[str, ...]] = {
     "attention_rotated": (),
     "routed_experts": (),
     "attention_sigmoid": (),
+    "attention_sigmoid_mma": (),
     "state_space": (),
 }
 

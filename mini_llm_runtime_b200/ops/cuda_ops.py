@@ -1490,6 +1490,9 @@ class CudaOps:
         return q
 
     SIGMOID_CHUNK_KEYS = 64       # keys one CTA of the sigmoid attention takes of a row, at least, when rows are few
+    SIGMOID_MMA_CHUNK_KEYS = 128  # the same for the tensor-core kernel
+    SIGMOID_MMA_LONGEST = 512     # keys one CTA of the tensor-core kernel takes of a row, at most
+    use_mma_sigmoid = True        # bfloat16 with key and value sizes of 64 or 128: the two products on the tensor cores
 
     def sigmoid_attention(self, q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, batch: AttentionBatch,
                           heads: int, kv_heads: int, dim: int, vdim: int, scale: float, *, distance=None,
@@ -1514,11 +1517,32 @@ class CudaOps:
                     raise KernelError(f"{name} has shape {tuple(vector.shape)}, expected {shape}")
         rows = q.shape[0]
         out = torch.empty((rows, heads * vdim), dtype=q.dtype, device=q.device)
+        tiles = batch.counts["tiles"]
+        if (self.use_mma_sigmoid and self.use_mma_attention and q.dtype == torch.bfloat16 and dim in (64, 128)
+                and vdim in (64, 128) and q.data_ptr() % 16 == 0):
+            mma = build.load_library("attention_sigmoid_mma")
+            if mma.mlr_attention_sigmoid_mma_fits(heads, kv_heads, dim, vdim):
+                # one CTA per entry of 16 rows and chunk of keys: steps of few rows share a row's keys out over
+                # several CTAs; and no CTA takes more than SIGMOID_MMA_LONGEST keys, so that the rows at the end
+                # of a long prompt (which see all of it) do not keep one SM busy long after the others
+                want = max(1, 2 * self.sm_count(q.device) // max(tiles, 1))
+                longest = int(batch.max_kv_len)
+                chunks = max(-(-longest // self.SIGMOID_MMA_LONGEST), min(want, -(-longest // self.SIGMOID_MMA_CHUNK_KEYS)), 1)
+                chunk_keys = max(32, -(-(-(-int(batch.max_kv_len) // chunks)) // 32) * 32)
+                partial = None
+                if chunks > 1:
+                    partial = torch.empty((chunks, rows, heads * vdim), dtype=torch.float32, device=q.device)
+                _check(mma.mlr_attention_sigmoid_mma(
+                    _ptr(q), _ptr(k_pool), _ptr(v_pool), _ptr(out), _ptr(partial), _ptr(batch.plan["tile_seg"]),
+                    _ptr(batch.plan["tile_row0"]), _ptr(batch.seg_q_start), _ptr(batch.seg_q_len), _ptr(batch.seg_pos0),
+                    _ptr(batch.block_table), _ptr(batch.seg_slot), batch.block_table.shape[1], tiles, rows, heads,
+                    kv_heads, dim, vdim, k_pool.shape[2], ctypes.c_float(scale), _ptr(r1), _ptr(r2), _ptr(score_bias),
+                    _ptr(head_mix), chunks, chunk_keys, _stream()), "sigmoid attention (tensor cores)")
+                return out
         lib = build.load_library("attention_sigmoid")
         per_cta = lib.mlr_attention_sigmoid_rows(heads, dim, vdim)
         if per_cta <= 0:
             raise KernelError("sigmoid attention: the heads are too many or too large for one CTA")
-        tiles = batch.counts["tiles"]
         # steps of few rows: the keys of a row are shared out over several CTAs, about three CTAs per SM in all
         # (a one-row segment's entry keeps one CTA busy, another entry 16 / per_cta of them)
         ctas = batch.num_decode + (tiles - batch.num_decode) * (16 // per_cta)

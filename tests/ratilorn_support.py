@@ -161,7 +161,8 @@ def take(want, index):
 
 def assert_logits_close(got, want, dtype, what="", limit=None):
     """Difference of the rows with their mean taken off, root mean square over the vocabulary, relative to
-    the logits' own spread: 2e-5 in 32-bit (order of additions only), 3e-2 in bfloat16.  A router's close
+    the logits' own spread: 2e-5 in 32-bit (order of additions only), 4e-2 in bfloat16 (the test models are
+    narrow: a rounding weighs more than in a wide one).  A router's close
     call may go the other way in the engine (its input is rounded; in 32-bit a gap of a millionth is
     enough): such rows are left out, and the rows behind them (which read them through the attention and
     the carried state) get ten times the allowance in bfloat16, which still tells a wrong kernel from a
@@ -169,7 +170,7 @@ def assert_logits_close(got, want, dtype, what="", limit=None):
     assert got.shape == want.shape, f"{what}: shape {tuple(got.shape)} against {tuple(want.shape)}"
     assert torch.isfinite(got).all(), f"{what}: non-finite logits"
     error = row_errors(got, want)
-    limit = limit or (2e-5 if dtype == torch.float32 else 3e-2)
+    limit = limit or (2e-5 if dtype == torch.float32 else 4e-2)
     margin = getattr(want, "margin", None)
     close = CLOSE_CALL_32 if dtype == torch.float32 else CLOSE_CALL
     if margin is not None and bool((margin < close).any()):

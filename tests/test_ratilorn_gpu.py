@@ -88,6 +88,72 @@ def test_router_kernel_against_its_formula():
         assert torch.allclose(weights.cpu().double(), picked / picked.sum(-1, keepdim=True), atol=1e-6)
 
 
+@pytest.mark.parametrize("heads,kv_heads,dim,vdim", [(4, 2, 64, 64), (16, 4, 128, 128), (14, 2, 64, 128), (3, 1, 128, 64),
+                                                     (6, 2, 24, 40), (5, 5, 10, 6)])
+def test_sigmoid_attention_kernels_against_their_formula(heads, kv_heads, dim, vdim):
+    """The float32 kernel, the bfloat16 kernel on the CUDA cores and (where the sizes allow it) the
+    tensor-core kernel against the formula, on a ragged batch over scattered pages: a portion behind 300
+    cached tokens, a portion from the start, and single rows far into their requests (their keys shared
+    out over several blocks)."""
+    import numpy as np
+
+    from mini_llm_runtime_b200.ops.cuda_ops import AttentionBatch, plan_attention
+
+    k = ops.current()
+    generator = torch.Generator().manual_seed(heads * 100 + dim)
+    lengths, starts = np.array([70, 33, 1, 1], dtype=np.int32), np.array([300, 0, 777, 64], dtype=np.int32)
+    page, pages_per_request = 16, 50
+    order = torch.randperm(4 * pages_per_request, generator=generator).to(torch.int32)
+    table = order.view(4, pages_per_request)
+    keys = torch.randn(4, 800, kv_heads, dim, generator=generator)
+    keys = keys / keys.pow(2).mean(-1, keepdim=True).sqrt()
+    values = torch.randn(4, 800, kv_heads, vdim, generator=generator)
+    rows = int(lengths.sum())
+    q = torch.randn(rows, heads, dim, generator=generator)
+    q = q / q.pow(2).mean(-1, keepdim=True).sqrt()
+    r1, r2 = torch.rand(heads, generator=generator), torch.rand(heads, generator=generator)
+    pb = torch.randn(heads, generator=generator) - 2.0
+    talk = torch.eye(heads) + 0.3 * torch.randn(heads, heads, generator=generator)
+    scale = 2.0 / math.sqrt(dim)
+    row_start = np.concatenate([[0], np.cumsum(lengths)[:-1]]).astype(np.int32)
+    arrays, counts = plan_attention(lengths, starts)
+
+    def dev(a, dtype=torch.int32):
+        return torch.as_tensor(a).to(device=DEVICE, dtype=dtype).contiguous()
+
+    batch = AttentionBatch(dev(row_start), dev(lengths), dev(starts), dev(np.arange(4)), dev(table), 4, int(lengths.max()),
+                           int((starts + lengths).max()), {n: dev(v) for n, v in arrays.items()}, counts)
+    for dtype, use_mma, limit in ((F32, False, 2e-5), (BF16, False, 1.5e-2), (BF16, True, 1.5e-2)):
+        k_pool = torch.zeros(4 * pages_per_request, kv_heads, page, dim, dtype=dtype)
+        v_pool = torch.zeros(4 * pages_per_request, kv_heads, page, vdim, dtype=dtype)
+        for request in range(4):
+            for position in range(800):
+                at = int(table[request, position // page])
+                k_pool[at, :, position % page] = keys[request, position].to(dtype)
+                v_pool[at, :, position % page] = values[request, position].to(dtype)
+        qd = q.to(dtype)
+        k.use_mma_sigmoid = use_mma
+        try:
+            got = k.sigmoid_attention(qd.view(rows, -1).to(DEVICE), k_pool.to(DEVICE), v_pool.to(DEVICE), batch, heads, kv_heads,
+                                      dim, vdim, scale, distance=(r1.to(DEVICE), r2.to(DEVICE)), score_bias=pb.to(DEVICE),
+                                      head_mix=talk.to(DEVICE))
+        finally:
+            k.use_mma_sigmoid = True
+        group = heads // kv_heads
+        for request in range(4):
+            for r in range(int(lengths[request])):
+                position = int(starts[request]) + r
+                kk = keys[request, :position + 1].to(dtype).double().repeat_interleave(group, dim=1)
+                vv = values[request, :position + 1].to(dtype).double().repeat_interleave(group, dim=1)
+                row = int(row_start[request]) + r
+                score = torch.einsum("hd,khd->hk", qd[row].double(), kk) * scale
+                distance = (position - torch.arange(position + 1)).double()
+                score = score - r1.double()[:, None] * torch.log1p(r2.double()[:, None] * distance[None]) + pb.double()[:, None]
+                want = torch.einsum("hk,khd->hd", talk.double() @ torch.sigmoid(score), vv).reshape(-1)
+                error = float((got[row].double().cpu() - want).abs().max()) / float(want.abs().max())
+                assert error < limit, f"{dtype}, tensor cores {use_mma}: request {request}, row {r}: off by {error:.2e}"
+
+
 def test_state_space_kernels_against_their_formulas():
     """Convolution, recurrence and gated norm on a ragged batch (a long portion, a single token, a
     portion shorter than the taps), then the same requests continued: the carried inputs and the state."""
