@@ -115,7 +115,9 @@ __device__ __forceinline__ void copy_async_commit() { asm volatile("cp.async.com
 template <int N> __device__ __forceinline__ void copy_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
 
 // SL: threads that share one value channel's state (a power of two; SL * SCAN_NPT >= n).  Lane l of a warp
-// holds entries [s * 16, s * 16 + 16) of channel p with s = l % SL, p = l / SL.
+// holds 16 entries of channel p = l / SL: the pieces of four entries number s, s + SL, s + 2 SL, s + 3 SL with
+// s = l % SL (neighbouring threads read neighbouring 16-byte pieces of a staged row: no bank conflicts; with
+// 16 entries in a row per thread a quarter warp's reads fell into two banks).
 // grid: (segments, heads, value-channel blocks).  The inputs of 32 tokens at a time are staged in shared
 // memory by asynchronous copies, the next 32 while these are walked; WIDE: in 16-byte pieces (state size,
 // channel block and all row strides multiples of four floats, pointers aligned).
@@ -177,10 +179,11 @@ state_space_scan_kernel(ScanArgs a) {
 
   stage(0, 0);
   float* state = a.states + (((size_t)a.seg_slot[seg] * a.heads + head) * P + (p < P ? p : 0)) * N;
+  auto entry = [&](int i) { return (((i >> 2) * SL + s) << 2) + (i & 3); };      // the state entry a thread's i-th number is
   float S[SCAN_NPT];
 #pragma unroll
   for (int i = 0; i < SCAN_NPT; ++i) {
-    const int n = s * SCAN_NPT + i;
+    const int n = entry(i);
     S[i] = (p < P && n < N) ? state[n] : 0.f;
   }
   int which = 0;
@@ -201,31 +204,33 @@ state_space_scan_kernel(ScanArgs a) {
       decay[threadIdx.x] = expf(-rate * dt);
     }
     __syncthreads();
+    // two tokens in flight: the second one's reads and products run under the first one's sums and shuffles
+#pragma unroll 2
     for (int t = 0; t < tokens; ++t) {
       const float av = decay[t], xv = p < P ? x_rows[t * P_CTA + p_local] : 0.f;
       const float dx = step[t] * xv;
-      const float* bt = b_rows + t * N + s * SCAN_NPT;
-      const float* ct = c_rows + t * N + s * SCAN_NPT;
+      const float* bt = b_rows + t * N;
+      const float* ct = c_rows + t * N;
       float bv[SCAN_NPT], cv[SCAN_NPT];
       if (WIDE) {
 #pragma unroll
         for (int i = 0; i < SCAN_NPT; i += 4) {
-          const float4 b4 = *reinterpret_cast<const float4*>(bt + i), c4 = *reinterpret_cast<const float4*>(ct + i);
+          const float4 b4 = *reinterpret_cast<const float4*>(bt + entry(i)), c4 = *reinterpret_cast<const float4*>(ct + entry(i));
           bv[i] = b4.x; bv[i + 1] = b4.y; bv[i + 2] = b4.z; bv[i + 3] = b4.w;
           cv[i] = c4.x; cv[i + 1] = c4.y; cv[i + 2] = c4.z; cv[i + 3] = c4.w;
         }
       } else {
 #pragma unroll
         for (int i = 0; i < SCAN_NPT; ++i) {
-          const bool in = s * SCAN_NPT + i < N;
-          bv[i] = in ? bt[i] : 0.f;
-          cv[i] = in ? ct[i] : 0.f;
+          const bool in = entry(i) < N;
+          bv[i] = in ? bt[entry(i)] : 0.f;
+          cv[i] = in ? ct[entry(i)] : 0.f;
         }
       }
       float sums[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
       for (int i = 0; i < SCAN_NPT; ++i) {
-        if (s * SCAN_NPT + i < N) {
+        if (entry(i) < N) {
           S[i] = fmaf(av, S[i], bv[i] * dx);
           sums[i & 3] = fmaf(S[i], cv[i], sums[i & 3]);
         }
@@ -240,7 +245,7 @@ state_space_scan_kernel(ScanArgs a) {
   if (p < P) {
 #pragma unroll
     for (int i = 0; i < SCAN_NPT; ++i) {
-      const int n = s * SCAN_NPT + i;
+      const int n = entry(i);
       if (n < N) state[n] = S[i];
     }
   }

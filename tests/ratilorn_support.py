@@ -263,17 +263,20 @@ class REngine:
         return {name: torch.cat(rows) for name, rows in got.items()}
 
 
-def dominant_key_case(length, query, key, seed, dim=12, vdim=10):
+def dominant_key_case(length, query, key, seed, dim=12, vdim=10, kv_heads=1):
     """A one-layer model (sigmoid attention, no feed-forward) whose weights let one chosen key carry
     nearly all the weight of one chosen query.  Token ids are the positions' own (vocabulary = length),
     position vectors are zero.  Keys are the first ``dim`` channels of the embedding, queries (both heads)
     the same channels rolled by one; the key's token embeds as the query's with those channels rolled,
     so that after the per-head norms q_query . k_key = dim while any other pair scores about sqrt(dim)
-    at most.  With a score scale of 2, a score bias of -14 and no distance bias, that key gets a weight
-    near 1 and every other key (the query's own included) one below 1e-3: the query's output is that
-    key's value, whenever the key is seen, however far back it lies."""
-    width = 40
-    cfg = config([attention(2, 1, dim, vdim, scale=2.0)], width=width, vocab=length, max_positions=length)
+    at most.  With a score scale of 24 / dim (2 at the default size), a score bias 10 below the matched
+    score and no distance bias, that key gets a weight near 1 and every other key (the query's own
+    included) a small one: the query's output is that key's value, whenever the key is seen, however far
+    back it lies."""
+    width = max(40, dim + 8)
+    scale = 24.0 / dim if dim <= 12 else 32.0 / dim
+    bias = -(scale * dim - 10.0)
+    cfg = config([attention(2 * kv_heads, kv_heads, dim, vdim, scale=scale)], width=width, vocab=length, max_positions=length)
     generator = torch.Generator().manual_seed(seed)
 
     def embed(table):
@@ -286,11 +289,14 @@ def dominant_key_case(length, query, key, seed, dim=12, vdim=10):
 
     def query_matrix(_):
         rolled = torch.cat([torch.roll(torch.eye(dim), 1, dims=0), torch.zeros(dim, width - dim)], dim=1)
-        return torch.cat([rolled, rolled])
+        return torch.cat([rolled] * (2 * kv_heads))
+
+    def key_matrices(_):
+        return torch.cat([key_matrix(_)] * kv_heads)
 
     zero = torch.zeros_like
-    overrides = {"embed": embed, "pos": zero, "l0.norm1": zero, "l0.mix.k": key_matrix, "l0.mix.q": query_matrix,
-                 "l0.mix.q.b": zero, "l0.mix.k.b": zero, "l0.mix.r1": zero, "l0.mix.pb": lambda t: torch.full_like(t, -14.0),
+    overrides = {"embed": embed, "pos": zero, "l0.norm1": zero, "l0.mix.k": key_matrices, "l0.mix.q": query_matrix,
+                 "l0.mix.q.b": zero, "l0.mix.k.b": zero, "l0.mix.r1": zero, "l0.mix.pb": lambda t: torch.full_like(t, bias),
                  "l0.mix.talk": lambda t: torch.eye(t.shape[0])}
     return cfg, overrides
 

@@ -299,6 +299,31 @@ def test_far_keys_and_page_borders_with_a_dominant_key(query, key, how):
     assert float((other[query] - want[query]).abs().max()) > 1e-2 * float(want[query].abs().max())
 
 
+@pytest.mark.parametrize("how", ["prompt", "decoded"])
+@pytest.mark.parametrize("query,key", [
+    (599, 511),     # the last key of the first 512: the end of a block's share of a long row
+    (599, 512),     # the first key of the next share
+    (590, 2),       # far back among hundreds
+    (530, 479),     # across a key tile's border
+])
+def test_far_keys_through_the_tensor_core_kernel(query, key, how):
+    """The same with heads of 64 in bfloat16, which the tensor-core kernel takes: a prompt of 600 tokens
+    is shared out over blocks in chunks of keys, decoded rows in smaller ones."""
+    length = 600
+    config, overrides = rs.dominant_key_case(length, query, key, seed=query + key, dim=64, vdim=64, kv_heads=2)
+    engine = rs.REngine(config, BF16, DEVICE, seed=5, overrides=overrides, num_pages=40, max_tokens=640)
+    tokens = list(range(length))
+    want = engine.plain(tokens)
+    cuts = {"prompt": [], "decoded": [520] + list(range(521, length))}[how]
+    got = engine.run_cuts("a", tokens, cuts)
+    rs.assert_logits_close(got[query:query + 1], want[query:query + 1], BF16, f"query {query}")
+    rs.assert_logits_close(got, want, BF16)
+    hidden = list(tokens)
+    hidden[key] = (key + 101) % length
+    other = engine.plain(hidden)
+    assert float((other[query] - want[query]).abs().max()) > 0.1 * float(want[query].abs().max())
+
+
 def test_the_distance_bias_counts_from_the_right_end():
     """A distance bias strong enough that only the nearest keys count: a distance that is one off, or
     taken from the wrong end, changes the answer."""
