@@ -33,8 +33,10 @@ struct SigmoidMmaArgs {
 };
 
 // grid: (work-list entries, key chunks)
+// Heads of 64 and 64 leave room for two blocks per SM (128 registers a thread: 64 of them output sums),
+// so that one block's barriers and dependent instructions pass under the other's work.
 template <int D, int V>
-__global__ void __launch_bounds__(SM_THREADS, 1)
+__global__ void __launch_bounds__(SM_THREADS, (D <= 64 && V <= 64) ? 2 : 1)
 attention_sigmoid_mma_kernel(const bf16* q, const bf16* k_pool, const bf16* v_pool, bf16* out, float* partial,
                              SigmoidMmaArgs a) {
   pdl_trigger();
@@ -46,6 +48,7 @@ attention_sigmoid_mma_kernel(const bf16* q, const bf16* k_pool, const bf16* v_po
   bf16* w_mix = v_tiles + (size_t)G * SM_KEYS * V;                         // [H][16][SM_WSTRIDE]
   float* w_raw = reinterpret_cast<float*>(w_mix + (size_t)H * SM_ROWS * SM_WSTRIDE);      // [H][16][SM_WSTRIDE]
   float* talk = w_raw + (size_t)H * SM_ROWS * SM_WSTRIDE;                  // [H][H]
+  int* key_row = reinterpret_cast<int*>(talk + H * H);                     // [2][32]: the cached row of every key of this and the next tile
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
 
   if (a.talk != nullptr)
@@ -68,22 +71,30 @@ attention_sigmoid_mma_kernel(const bf16* q, const bf16* k_pool, const bf16* v_po
     *reinterpret_cast<uint4*>(tile_at<D>(q_tiles + (size_t)h * SM_ROWS * D, r, chunk)) = value;
   }
 
-  // all key (or value) heads' rows of the tile at k0; keys past the rows' last position become zeros
-  auto fetch = [&](bool values, int k0) {
+  // the cached row (without the head) of every key of the tile at k0: page * G * page_size + place in the page;
+  // -1 for keys past the rows' last position and pages the request does not hold
+  auto find_rows = [&](int k0, int parity) {
+    if (warp == 0) {
+      const int key = k0 + lane;
+      int row = -1;
+      if (key <= last_pos) {
+        const int page = table[key / a.page_size];
+        if (page >= 0) row = page * G * a.page_size + key % a.page_size;
+      }
+      key_row[parity * SM_KEYS + lane] = row;
+    }
+  };
+  // all key (or value) heads' rows of a tile whose keys' rows are known; missing keys become zeros
+  auto fetch = [&](bool values, int parity) {
     const int W = values ? V : D;
     const bf16* pool = values ? v_pool : k_pool;
     bf16* tiles = values ? v_tiles : k_tiles;
     const int chunks = W / 8;
     for (int item = threadIdx.x; item < G * SM_KEYS * chunks; item += SM_THREADS) {
       const int chunk = item % chunks, r = (item / chunks) % SM_KEYS, c = item / (chunks * SM_KEYS);
-      const int key = k0 + r;
-      bool valid = key <= last_pos;
-      const bf16* src = pool;
-      if (valid) {
-        const int page = table[key / a.page_size];
-        valid = page >= 0;
-        if (valid) src = pool + (((size_t)page * G + c) * a.page_size + key % a.page_size) * W + chunk * 8;
-      }
+      const int row = key_row[parity * SM_KEYS + r];
+      const bool valid = row >= 0;
+      const bf16* src = valid ? pool + ((size_t)row + (size_t)c * a.page_size) * W + chunk * 8 : pool;
       bf16* dst = values ? tile_at<V>(tiles + (size_t)c * SM_KEYS * V, r, chunk) : tile_at<D>(tiles + (size_t)c * SM_KEYS * D, r, chunk);
       cp_async_16(dst, src, valid);
     }
@@ -97,11 +108,15 @@ attention_sigmoid_mma_kernel(const bf16* q, const bf16* k_pool, const bf16* v_po
     for (int t = 0; t < V / 8; ++t) o[hi][t][0] = o[hi][t][1] = o[hi][t][2] = o[hi][t][3] = 0.f;
 
   if (chunk_first <= chunk_last) {
-    fetch(false, chunk_first);
-    fetch(true, chunk_first);
+    find_rows(chunk_first, 0);
+    __syncthreads();
+    fetch(false, 0);
+    fetch(true, 0);
   }
-  for (int k0 = chunk_first; k0 <= chunk_last; k0 += SM_KEYS) {
+  int parity = 0;
+  for (int k0 = chunk_first; k0 <= chunk_last; k0 += SM_KEYS, parity ^= 1) {
     const bool more = k0 + SM_KEYS <= chunk_last;
+    if (more) find_rows(k0 + SM_KEYS, parity ^ 1);      // seen after the barriers below, before the next tile is asked for
     cp_async_wait<1>();      // this tile's keys (its values may still be on their way)
     __syncthreads();
     // ---- every head's own weights: warp w takes heads w, w + 8
@@ -146,7 +161,7 @@ attention_sigmoid_mma_kernel(const bf16* q, const bf16* k_pool, const bf16* v_po
       }
     }
     __syncthreads();
-    if (more) fetch(false, k0 + SM_KEYS); else cp_async_commit();
+    if (more) fetch(false, parity ^ 1); else cp_async_commit();
     // ---- the weights mixed across the heads, rounded to bfloat16 for the second product
     for (int idx = threadIdx.x; idx < H * SM_ROWS * (SM_KEYS / 2); idx += SM_THREADS) {
       const int j = (idx % (SM_KEYS / 2)) * 2, r = (idx / (SM_KEYS / 2)) % SM_ROWS, h = idx / ((SM_KEYS / 2) * SM_ROWS);
@@ -195,7 +210,7 @@ attention_sigmoid_mma_kernel(const bf16* q, const bf16* k_pool, const bf16* v_po
       }
     }
     __syncthreads();
-    if (more) fetch(true, k0 + SM_KEYS); else cp_async_commit();
+    if (more) fetch(true, parity ^ 1); else cp_async_commit();
   }
   cp_async_wait<0>();
 
@@ -234,7 +249,7 @@ add_chunks_bf16_kernel(const float* partial, bf16* __restrict__ out, long long c
 static size_t sigmoid_mma_shared(int heads, int kv_heads, int dim, int vdim) {
   return sizeof(bf16) * ((size_t)heads * SM_ROWS * dim + (size_t)kv_heads * SM_KEYS * (dim + vdim) +
                          (size_t)heads * SM_ROWS * SM_WSTRIDE) +
-         sizeof(float) * ((size_t)heads * SM_ROWS * SM_WSTRIDE + (size_t)heads * heads);
+         sizeof(float) * ((size_t)heads * SM_ROWS * SM_WSTRIDE + (size_t)heads * heads) + sizeof(int) * 2 * SM_KEYS;
 }
 
 }  // namespace mlr
