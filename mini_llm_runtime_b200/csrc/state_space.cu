@@ -60,19 +60,28 @@ causal_conv_kernel(const float* u, long long u_stride, const float* __restrict__
   const int t0 = blockIdx.z * CONV_TOKENS;
   if (t0 >= q_len) return;
   float* state = states + (size_t)seg_slot[seg] * (taps - 1) * channels;
-  const int t_end = min(q_len, t0 + CONV_TOKENS);
-  for (int t = t0; t < t_end; ++t) {
-    float sum = b;
+  const int count = min(q_len - t0, CONV_TOKENS);
+  // every input the thread's tokens need, asked for at once (one trip to memory): the tokens' own and the
+  // taps - 1 before them, which for the segment's first tokens come from the carried inputs
+  float in[CONV_TOKENS + MAX_TAPS - 1];
 #pragma unroll
-    for (int k = 0; k < MAX_TAPS; ++k) {
-      if (k < taps) {
-        const int s = t - (taps - 1) + k;
-        const float v = s >= 0 ? __ldcg(u + (size_t)(q_start + s) * u_stride + c) : state[(size_t)(taps - 1 + s) * channels + c];
-        sum = fmaf(w[k], v, sum);
-      }
+  for (int i = 0; i < CONV_TOKENS + MAX_TAPS - 1; ++i) {
+    in[i] = 0.f;
+    if (i < count + taps - 1) {
+      const int s = t0 - (taps - 1) + i;
+      in[i] = s >= 0 ? __ldcg(u + (size_t)(q_start + s) * u_stride + c) : state[(size_t)(taps - 1 + s) * channels + c];
     }
-    if (act == 1) sum = sum / (1.f + expf(-sum));
-    out[(size_t)(q_start + t) * channels + c] = sum;
+  }
+#pragma unroll
+  for (int t = 0; t < CONV_TOKENS; ++t) {
+    if (t < count) {
+      float sum = b;
+#pragma unroll
+      for (int k = 0; k < MAX_TAPS; ++k)
+        if (k < taps) sum = fmaf(w[k], in[t + k], sum);
+      if (act == 1) sum = sum / (1.f + expf(-sum));
+      out[(size_t)(q_start + t0 + t) * channels + c] = sum;
+    }
   }
   if (q_len == 1) carry_inputs(u, u_stride, state, channels, c, q_start, q_len, taps);
 }
